@@ -1,0 +1,87 @@
+"""Builds libqvx_cuda.so (sm_100a) in-tree with nvcc.  `python -m qubivex_b200.build`.
+
+Each source is compiled to an object under build/ and the objects are linked into
+qubivex_b200/lib/libqvx_cuda.so with the static CUDA runtime, so the library has no
+dependency the GPU box could miss.  Only attn_exact.cu is built with -fmad=false: its
+arithmetic must keep the reference's operation order (no contraction).
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+LIB = PKG / "lib" / "libqvx_cuda.so"
+OBJ = ROOT / "build" / "obj"
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
+SOURCES = {
+    "qvx_api.cu": [],
+    "kv_rows.cu": [],
+    "block_copy.cu": [],
+    "attn_split.cu": [],
+    "attn_exact.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],
+    "runtime.cpp": [],
+}
+
+
+def nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found: the CUDA backend cannot be built")
+    return exe
+
+
+def _stale(target: Path, deps: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    OBJ.mkdir(parents=True, exist_ok=True)
+    LIB.parent.mkdir(parents=True, exist_ok=True)
+    headers = list(CSRC.glob("*.cuh")) + [ROOT / "include" / "qvx.h", Path(__file__)]
+    jobs = []
+    for name, extra in SOURCES.items():
+        src = CSRC / name
+        obj = OBJ / (name.rsplit(".", 1)[0] + ".o")
+        if force or _stale(obj, [src] + headers):
+            cmd = [nvcc(), *ARCH, *COMMON, *extra]
+            if verbose:
+                cmd += ["-Xptxas", "-v"]
+            cmd += ["-c", str(src), "-o", str(obj)]
+            jobs.append((name, cmd))
+
+    def run(job):
+        name, cmd = job
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        return name, r
+
+    with ThreadPoolExecutor(max_workers=min(6, max(1, len(jobs)))) as ex:
+        for name, r in ex.map(run, jobs):
+            if verbose or r.returncode:
+                sys.stderr.write(f"--- {name}\n{r.stdout}{r.stderr}")
+            if r.returncode:
+                raise RuntimeError(f"nvcc failed on {name}")
+    objs = [OBJ / (n.rsplit(".", 1)[0] + ".o") for n in SOURCES]
+    if force or jobs or _stale(LIB, objs):
+        cmd = [nvcc(), *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("link failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    out = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(out)

@@ -1,0 +1,108 @@
+// KV sync and KV append: one position's key row and value row (f32, kv_out each) written
+// into its block of the pool, narrowed to the pool's element type.
+//
+// Replaces the `put` closure of the reference's CPU device
+// (crates/qubivex-backend-cpu/src/sim.rs:377-399), `kv_sync.comp`
+// (crates/qubivex-backend-vulkan/shaders/kv_sync.comp:36-50) and the store of
+// `attn_prelude.comp` (shaders/attn_prelude.comp:92-104, :169-173).
+//
+// Native layout: one thread per 16-byte chunk of the pool — a row of d elements is d*e/16
+// consecutive chunks, so a warp writes whole rows with 16-byte vector stores.
+// Algorithmic bytes per row pair: 2 * kv_out * (4 + e).
+// Reference layout: keys are dimension-major inside a block, a stride-B scatter of single
+// elements; one thread per element (compatibility path, not the fast one).
+#include "qvx_common.cuh"
+
+namespace qvx {
+
+struct RowArgs {
+    Layout L;
+    uint8_t* pool;
+    const float* k_rows;
+    const float* v_rows;
+    size_t row_stride;          // floats between consecutive rows of k_rows / v_rows
+    const uint32_t* at_direct;  // sync: pool position per row (0xffffffff: skip); else null
+    const uint32_t* pos;        // append: position, table start and tables
+    const uint32_t* blocks;
+    const uint32_t* table_at;
+    uint32_t n;
+};
+
+__device__ __forceinline__ bool row_target(const RowArgs& a, uint32_t r, uint32_t& block, uint32_t& slot) {
+    if (a.at_direct) {
+        uint32_t at = a.at_direct[r];
+        if (at == 0xffffffffu) return false;
+        block = at / a.L.B; slot = at % a.L.B;
+    } else {
+        uint32_t p = a.pos[r];
+        block = a.blocks[a.table_at[r] + p / a.L.B];
+        slot = p % a.L.B;
+    }
+    return true;
+}
+
+// grid: ceil(n * kvh * 2 * chunks_per_row / 256) x 256 threads.
+__global__ void __launch_bounds__(256) kv_rows_native_kernel(RowArgs a) {
+    const uint32_t cpr = a.L.row_bytes >> 4;  // chunks per row
+    const uint32_t per_row = a.L.kvh * 2u * cpr;
+    uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)a.n * per_row) return;
+    uint32_t r = (uint32_t)(idx / per_row), w = (uint32_t)(idx % per_row);
+    uint32_t g = w / (2u * cpr), kv = (w / cpr) & 1u, c = w % cpr;
+    uint32_t block, slot;
+    if (!row_target(a, r, block, slot)) return;
+    const uint32_t epc = 16u / a.L.e;  // elements per chunk
+    const float* src = (kv ? a.v_rows : a.k_rows) + (size_t)r * a.row_stride + g * a.L.d + c * epc;
+    uint4 out;
+    if (a.L.dtype == QVX_F32) {
+        out = *reinterpret_cast<const uint4*>(src);
+    } else {
+        float4 lo = *reinterpret_cast<const float4*>(src);
+        float4 hi = *reinterpret_cast<const float4*>(src + 4);
+        uint32_t dt = a.L.dtype;
+        out.x = (uint32_t)narrow16(lo.x, dt) | ((uint32_t)narrow16(lo.y, dt) << 16);
+        out.y = (uint32_t)narrow16(lo.z, dt) | ((uint32_t)narrow16(lo.w, dt) << 16);
+        out.z = (uint32_t)narrow16(hi.x, dt) | ((uint32_t)narrow16(hi.y, dt) << 16);
+        out.w = (uint32_t)narrow16(hi.z, dt) | ((uint32_t)narrow16(hi.w, dt) << 16);
+    }
+    uint8_t* dst = a.pool + (uint64_t)block * a.L.block_bytes + (uint64_t)g * 2u * a.L.page_bytes +
+                   (uint64_t)kv * a.L.page_bytes + (uint64_t)slot * a.L.row_bytes + ((c ^ (slot & 7u)) << 4);
+    *reinterpret_cast<uint4*>(dst) = out;
+}
+
+// Any layout, one thread per element.
+__global__ void __launch_bounds__(256) kv_rows_element_kernel(RowArgs a) {
+    const uint32_t kv_out = a.L.kvh * a.L.d;
+    uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (uint64_t)a.n * 2u * kv_out) return;
+    uint32_t r = (uint32_t)(idx / (2u * kv_out)), w = (uint32_t)(idx % (2u * kv_out));
+    uint32_t kv = w / kv_out, gi = w % kv_out, g = gi / a.L.d, i = gi % a.L.d;
+    uint32_t block, slot;
+    if (!row_target(a, r, block, slot)) return;
+    float x = (kv ? a.v_rows : a.k_rows)[(size_t)r * a.row_stride + gi];
+    uint8_t* dst = a.pool + (uint64_t)block * a.L.block_bytes + in_block_offset(a.L, slot, kv, g, i);
+    if (a.L.dtype == QVX_F32) *reinterpret_cast<float*>(dst) = x;
+    else *reinterpret_cast<uint16_t*>(dst) = narrow16(x, a.L.dtype);
+}
+
+int32_t launch_kv_rows(qvx_device* dev, const Layout& L, void* pool, const float* k_rows,
+                       const float* v_rows, size_t row_stride_f32, const uint32_t* at_direct,
+                       const uint32_t* pos, const uint32_t* blocks, const uint32_t* table_at, size_t n,
+                       int kind, cudaStream_t s) {
+    if (n == 0) return QVX_OK;
+    if (n > 0x7fffffffu) return fail(dev, QVX_ERR_CORE, "kv rows: %zu rows do not fit 31 bits", n);
+    RowArgs a{L, (uint8_t*)pool, k_rows, v_rows, row_stride_f32, at_direct, pos, blocks, table_at, (uint32_t)n};
+    LaunchTimer timer(dev, kind, s);
+    bool aligned = (((uintptr_t)k_rows | (uintptr_t)v_rows | (uintptr_t)pool) & 15u) == 0 &&
+                   (row_stride_f32 * 4) % 16 == 0;
+    if (L.layout == QVX_LAYOUT_NATIVE && aligned) {
+        uint64_t total = (uint64_t)n * L.kvh * 2u * (L.row_bytes >> 4);
+        kv_rows_native_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+    } else {
+        uint64_t total = (uint64_t)n * 2u * L.kvh * L.d;
+        kv_rows_element_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+    }
+    return check_cuda(dev, cudaGetLastError(), "kv rows launch");
+}
+
+}  // namespace qvx

@@ -1,0 +1,792 @@
+// The C ABI of libqvx_cuda: the device handle (the DiscreteDevice subset of
+// crates/qubivex-compute/src/discrete.rs:433-570 that the decode-attention stage uses),
+// buffers, block tables, and the op with host memory in and out.  Validation follows the
+// reference's CPU device (crates/qubivex-backend-cpu/src/sim.rs:313-324, :359-376).
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <chrono>
+#include <unordered_set>
+
+#include "qvx_common.cuh"
+
+namespace qvx {
+
+static thread_local std::string g_last_error;  // errors with no device to hang them on
+
+int32_t fail(qvx_device* dev, int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (dev) dev->last_error = buf;
+    g_last_error = buf;
+    return code;
+}
+
+int32_t check_cuda(qvx_device* dev, cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return QVX_OK;
+    return fail(dev, QVX_ERR_DEVICE, "cuda device error: %s: %s", what, cudaGetErrorString(e));
+}
+
+static uint64_t now_ns() {
+    return (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(
+               std::chrono::steady_clock::now().time_since_epoch())
+        .count();
+}
+
+// ---- launch timing ---------------------------------------------------------------------------
+LaunchTimer::LaunchTimer(qvx_device* dev, int kind, cudaStream_t s) : dev(dev), kind(kind), s(s) {
+    if (!dev || !dev->cfg.timing) return;
+    auto get = [&]() {
+        cudaEvent_t e = nullptr;
+        if (!dev->event_pool.empty()) { e = dev->event_pool.back(); dev->event_pool.pop_back(); }
+        else cudaEventCreate(&e);
+        return e;
+    };
+    a = get(); b = get();
+    cudaEventRecord(a, s);
+}
+LaunchTimer::~LaunchTimer() {
+    if (!a) return;
+    cudaEventRecord(b, s);
+    dev->pending.push_back(TimedLaunch{kind, a, b});
+}
+
+static void drain_timers(qvx_device* dev) {
+    for (auto& p : dev->pending) {
+        cudaEventSynchronize(p.b);
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, p.a, p.b) == cudaSuccess) {
+            dev->ktimes.launches[p.kind]++;
+            uint64_t ns = (uint64_t)((double)ms * 1e6);
+            dev->ktimes.gpu_ns[p.kind] += ns;
+            dev->xfer.timed++;
+            dev->xfer.gpu_ns += ns;
+            dev->xfer.gpu_busy_ns += ns;  // one stream: the launches do not overlap
+        }
+        dev->event_pool.push_back(p.a);
+        dev->event_pool.push_back(p.b);
+    }
+    dev->pending.clear();
+}
+
+// The status word lives in mapped pinned memory: kernels write it, the host reads it with no copy.
+struct DeviceExtras {
+    int* status_host = nullptr;
+    int* status_dev = nullptr;
+    cudaStream_t h2d = nullptr, d2h = nullptr;
+    std::vector<cudaEvent_t> sync_events;
+    size_t next_event = 0;
+};
+static std::mutex g_extras_mu;
+static std::vector<std::pair<qvx_device*, DeviceExtras*>> g_extras;
+static DeviceExtras* extras(qvx_device* dev) {
+    std::lock_guard<std::mutex> lk(g_extras_mu);
+    for (auto& p : g_extras)
+        if (p.first == dev) return p.second;
+    return nullptr;
+}
+int* device_status_word(qvx_device* dev) { return extras(dev)->status_dev; }
+
+static int32_t check_status(qvx_device* dev) {
+    DeviceExtras* x = extras(dev);
+    int st = *(volatile int*)x->status_host;
+    if (st == 0) return QVX_OK;
+    *(volatile int*)x->status_host = 0;
+    return fail(dev, QVX_ERR_DEVICE, "cuda device error: a kernel gave up a bounded wait (status %d); its outputs are not valid", st);
+}
+
+// ---- capacity accounting, as SimDevice::reserve (sim.rs:176-203) -----------------------------
+static int32_t reserve(qvx_device* dev, uint64_t bytes) {
+    uint64_t next = dev->usage.used + bytes;
+    if (next < dev->usage.used || next > dev->usage.capacity) {
+        dev->usage.refused++;
+        return fail(dev, QVX_ERR_OUT_OF_MEMORY, "cuda device is out of memory: %llu bytes requested, %llu of %llu in use",
+                    (unsigned long long)bytes, (unsigned long long)dev->usage.used,
+                    (unsigned long long)dev->usage.capacity);
+    }
+    dev->usage.used = next;
+    dev->usage.peak = std::max(dev->usage.peak, next);
+    return QVX_OK;
+}
+
+static int32_t new_buffer(qvx_device* dev, size_t len, bool arena, qvx_buffer** out) {
+    int32_t rc = reserve(dev, len);
+    if (rc) return rc;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, len ? len : 1);
+    if (e != cudaSuccess) {
+        dev->usage.used -= len;
+        cudaGetLastError();
+        return fail(dev, QVX_ERR_DEVICE, "cuda device error: cannot allocate %zu bytes: %s", len, cudaGetErrorString(e));
+    }
+    *out = new qvx_buffer{dev, p, len, arena, 1};
+    return QVX_OK;
+}
+
+static int32_t buffer_of(qvx_device* dev, qvx_buffer* b) {
+    if (!b || b->dev != dev) return fail(dev, QVX_ERR_DEVICE, "cuda device error: the buffer belongs to another device");
+    return QVX_OK;
+}
+
+// ---- staging for the host ops ---------------------------------------------------------------
+static int32_t ensure_staging(qvx_device* dev, size_t need) {
+    if (dev->staging_cap - dev->staging_used >= need && dev->dstaging_cap == dev->staging_cap) return QVX_OK;
+    return QVX_DECLINED;  // the caller drains the device and grows or resets
+}
+
+static int32_t grow_staging(qvx_device* dev, size_t need) {
+    // Only called with nothing in flight.
+    size_t cap = std::max<size_t>(need, std::max<size_t>(dev->staging_cap * 2, 8u << 20));
+    if (dev->staging) cudaFreeHost(dev->staging);
+    if (dev->dstaging) cudaFree(dev->dstaging);
+    dev->staging = nullptr; dev->dstaging = nullptr; dev->staging_cap = dev->dstaging_cap = 0;
+    cudaError_t e = cudaHostAlloc((void**)&dev->staging, cap, cudaHostAllocDefault);
+    if (e != cudaSuccess) return check_cuda(dev, e, "pinned staging");
+    e = cudaMalloc((void**)&dev->dstaging, cap);
+    if (e != cudaSuccess) return check_cuda(dev, e, "device staging");
+    dev->staging_cap = dev->dstaging_cap = cap;
+    dev->staging_used = 0;
+    return QVX_OK;
+}
+
+static int32_t wait_locked(qvx_device* dev) {
+    uint64_t t0 = now_ns();
+    DeviceExtras* x = extras(dev);
+    cudaError_t e = cudaStreamSynchronize(x->h2d);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(x->d2h);
+    dev->xfer.wait_ns += now_ns() - t0;
+    dev->xfer.fence_waits++;
+    dev->staging_used = 0;
+    x->next_event = 0;
+    for (qvx_tables* t : dev->inflight_tables) delete t;
+    dev->inflight_tables.clear();
+    if (e != cudaSuccess) return check_cuda(dev, e, "wait");
+    return check_status(dev);
+}
+
+static cudaEvent_t next_event(DeviceExtras* x) {
+    if (x->next_event == x->sync_events.size()) {
+        cudaEvent_t e;
+        cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+        x->sync_events.push_back(e);
+    }
+    return x->sync_events[x->next_event++];
+}
+
+// ---- tables ----------------------------------------------------------------------------------
+static uint32_t chunk_tokens_for(const Layout& L) {
+    static const uint32_t configured = [] {
+        const char* v = getenv("QVX_CHUNK_TOKENS");
+        long n = v ? atol(v) : 0;
+        return (uint32_t)(n > 0 ? n : 256);
+    }();
+    uint32_t c = std::max(configured, L.B) / L.B * L.B;
+    while (c > 2048 && c > L.B) c -= L.B;
+    return c;
+}
+
+struct TableImage {
+    size_t off_pos, off_table_at, off_blocks, off_part_at, off_items, bytes;
+    size_t n_items, n_parts;
+    uint32_t max_pos, chunk_blocks;
+};
+
+static int32_t validate_tables(qvx_device* dev, const Layout& L, size_t pool_blocks, size_t heads, size_t s,
+                               const uint32_t* pos, const uint32_t* blocks, size_t n_blocks,
+                               const uint32_t* table_at) {
+    if (heads == 0 || heads % L.kvh != 0)
+        return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: %zu tokens, %zu heads, %u KV heads of %u",
+                    s, heads, L.kvh, L.d);
+    if (s > 65535) return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: %zu tokens in one op (at most 65535)", s);
+    if (n_blocks > 0x7fffffffu) return fail(dev, QVX_ERR_CORE, "block tables of %zu entries", n_blocks);
+    for (size_t i = 0; i < n_blocks; i++)
+        if (blocks[i] >= pool_blocks)
+            return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: a block past the pool's %zu", pool_blocks);
+    for (size_t t = 0; t < s; t++)
+        if ((size_t)table_at[t] + pos[t] / L.B >= n_blocks)
+            return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: token %zu has no block for position %u",
+                        t, pos[t]);
+    return QVX_OK;
+}
+
+static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint32_t* pos, size_t n_blocks,
+                             bool split) {
+    TableImage im{};
+    uint32_t chunk = chunk_tokens_for(L);
+    im.chunk_blocks = chunk / L.B;
+    size_t group = heads / L.kvh, groups = L.kvh * ((group + 7) / 8);
+    for (size_t t = 0; t < s; t++) {
+        im.max_pos = std::max(im.max_pos, pos[t]);
+        if (!split) continue;
+        size_t nch = ((size_t)pos[t] + chunk) / chunk;
+        im.n_items += nch * groups;
+        if (nch > 1) im.n_parts += nch * groups;
+    }
+    size_t off = 0;
+    im.off_pos = off; off += 4 * s;
+    im.off_table_at = off; off += 4 * s;
+    im.off_blocks = off; off += 4 * n_blocks;
+    im.off_part_at = off; off += 4 * s;
+    off = (off + 15) & ~(size_t)15;
+    im.off_items = off; off += sizeof(qvx_item) * im.n_items;
+    im.bytes = (off + 255) & ~(size_t)255;
+    return im;
+}
+
+static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size_t heads, size_t s,
+                       const uint32_t* pos, const uint32_t* blocks, size_t n_blocks, const uint32_t* table_at) {
+    memcpy(img + im.off_pos, pos, 4 * s);
+    memcpy(img + im.off_table_at, table_at, 4 * s);
+    memcpy(img + im.off_blocks, blocks, 4 * n_blocks);
+    uint32_t* part_at = (uint32_t*)(img + im.off_part_at);
+    qvx_item* items = (qvx_item*)(img + im.off_items);
+    if (im.n_items == 0) {
+        for (size_t t = 0; t < s; t++) part_at[t] = 0xffffffffu;
+        return;
+    }
+    const uint32_t chunk = im.chunk_blocks * L.B;
+    const uint32_t group = (uint32_t)(heads / L.kvh), gpk = (group + 7) / 8, groups = L.kvh * gpk;
+    size_t n = 0;
+    uint32_t part = 0;
+    for (size_t t = 0; t < s; t++) {
+        uint32_t len = pos[t] + 1u, nch = (len + chunk - 1) / chunk;
+        part_at[t] = nch > 1 ? part : 0xffffffffu;
+        for (uint32_t grp = 0; grp < groups; grp++) {
+            uint32_t kvh = grp / gpk, sub = grp % gpk;
+            for (uint32_t c = 0; c < nch; c++) {
+                qvx_item& it = items[n++];
+                it.seq = (uint32_t)t;
+                it.first = table_at[t] + c * im.chunk_blocks;
+                it.tokens = std::min(chunk, len - c * chunk);
+                it.count = (it.tokens + L.B - 1) / L.B;
+                it.head0 = kvh * group + sub * 8;
+                it.nheads = std::min(8u, group - sub * 8);
+                it.kv_head = kvh;
+                it.part = nch > 1 ? part + grp * nch + c : 0xffffffffu;
+            }
+        }
+        if (nch > 1) part += nch * groups;
+    }
+    // Longest first, so the short tails fill the end of the launch.  Stable: the order is a
+    // function of the lengths alone.
+    std::stable_sort(items, items + n, [](const qvx_item& a, const qvx_item& b) { return a.tokens > b.tokens; });
+}
+
+static void bind_image(qvx_tables* t, const TableImage& im, void* dmem) {
+    uint8_t* d = (uint8_t*)dmem;
+    t->dmem = dmem; t->dmem_bytes = im.bytes;
+    t->d_pos = (uint32_t*)(d + im.off_pos);
+    t->d_table_at = (uint32_t*)(d + im.off_table_at);
+    t->d_blocks = (uint32_t*)(d + im.off_blocks);
+    t->d_part_at = (uint32_t*)(d + im.off_part_at);
+    t->d_items = (qvx_item*)(d + im.off_items);
+    t->n_items = im.n_items; t->n_parts = im.n_parts; t->max_pos = im.max_pos; t->chunk_blocks = im.chunk_blocks;
+}
+
+static int32_t ensure_partials(qvx_device* dev, size_t floats) {
+    if (floats * 4 <= dev->partials_cap) return QVX_OK;
+    // Work queued earlier may still read the old scratch.
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return check_cuda(dev, e, "partials");
+    if (dev->partials) cudaFree(dev->partials);
+    dev->partials = nullptr; dev->partials_cap = 0;
+    size_t cap = std::max<size_t>(floats * 4 * 5 / 4, 1u << 20);
+    e = cudaMalloc(&dev->partials, cap);
+    if (e != cudaSuccess) return check_cuda(dev, e, "partials");
+    dev->partials_cap = cap;
+    return QVX_OK;
+}
+
+static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
+                             uint32_t variant, cudaStream_t s) {
+    bool split_ok = attn_split_supported(t->L, t->heads) && t->n_items > 0;
+    if (variant == QVX_ATTN_SPLIT && !attn_split_supported(t->L, t->heads))
+        return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no split attention kernel for this geometry");
+    if (variant == QVX_ATTN_EXACT || !split_ok) return launch_attn_exact(dev, t, pool, q, out, s);
+    int32_t rc = ensure_partials(dev, attn_partial_floats(t));
+    if (rc) return rc;
+    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, s);
+}
+
+}  // namespace qvx
+
+using namespace qvx;
+
+// =================================================================================================
+extern "C" {
+
+size_t qvx_block_bytes(const qvx_geometry* geo) { return geometry_ok(geo) ? (size_t)make_layout(geo).block_bytes : 0; }
+
+size_t qvx_elem_offset(const qvx_geometry* geo, size_t at, int kv, size_t g, size_t i) {
+    Layout L = make_layout(geo);
+    return (at / L.B) * (size_t)L.block_bytes + in_block_offset(L, (uint32_t)(at % L.B), kv ? 1u : 0u, (uint32_t)g, (uint32_t)i);
+}
+
+const char* qvx_name(void) { return "cuda"; }
+
+int32_t qvx_open(const qvx_config* cfg, qvx_device** out) {
+    if (!out) return QVX_ERR_SHAPE;
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(nullptr, QVX_ERR_DEVICE, "cuda device error: no CUDA device (%s); this backend has no CPU path",
+                    e == cudaSuccess ? "count is 0" : cudaGetErrorString(e));
+    }
+    int ord = cfg ? cfg->device : 0;
+    if (ord < 0 || ord >= n) return fail(nullptr, QVX_ERR_DEVICE, "cuda device error: no device %d (%d present)", ord, n);
+    if ((e = cudaSetDevice(ord)) != cudaSuccess) return check_cuda(nullptr, e, "cudaSetDevice");
+    qvx_device* dev = new qvx_device;
+    dev->ordinal = ord;
+    if (cfg) dev->cfg = *cfg;
+    cudaGetDeviceProperties(&dev->prop, ord);
+    if (dev->prop.major < 9) {
+        int major = dev->prop.major, minor = dev->prop.minor;
+        delete dev;
+        return fail(nullptr, QVX_ERR_UNSUPPORTED, "cuda backend is built for sm_100a; device %d is sm_%d%d", ord, major, minor);
+    }
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    dev->usage.capacity = dev->cfg.capacity ? dev->cfg.capacity : free_b;
+    DeviceExtras* x = new DeviceExtras;
+    e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&x->h2d, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&x->d2h, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&x->status_host, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        *x->status_host = 0;
+        e = cudaHostGetDevicePointer((void**)&x->status_dev, x->status_host, 0);
+    }
+    if (e != cudaSuccess) {
+        delete x; delete dev;
+        return check_cuda(nullptr, e, "open");
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_extras_mu);
+        g_extras.emplace_back(dev, x);
+    }
+    *out = dev;
+    return QVX_OK;
+}
+
+void qvx_close(qvx_device* dev) {
+    if (!dev) return;
+    cudaSetDevice(dev->ordinal);
+    cudaDeviceSynchronize();
+    {
+        std::lock_guard<std::mutex> lk(dev->mu);
+        drain_timers(dev);
+        for (qvx_tables* t : dev->inflight_tables) delete t;
+        dev->inflight_tables.clear();
+    }
+    for (cudaEvent_t ev : dev->event_pool) cudaEventDestroy(ev);
+    if (dev->partials) cudaFree(dev->partials);
+    if (dev->staging) cudaFreeHost(dev->staging);
+    if (dev->dstaging) cudaFree(dev->dstaging);
+    DeviceExtras* x = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_extras_mu);
+        for (size_t i = 0; i < g_extras.size(); i++)
+            if (g_extras[i].first == dev) { x = g_extras[i].second; g_extras.erase(g_extras.begin() + i); break; }
+    }
+    if (x) {
+        for (cudaEvent_t ev : x->sync_events) cudaEventDestroy(ev);
+        cudaStreamDestroy(x->h2d); cudaStreamDestroy(x->d2h);
+        cudaFreeHost(x->status_host);
+        delete x;
+    }
+    cudaStreamDestroy(dev->stream);
+    delete dev;
+}
+
+int32_t qvx_describe(qvx_device* dev, char* out, size_t cap) {
+    if (!dev || !out || !cap) return QVX_ERR_SHAPE;
+    snprintf(out, cap, "%s (sm_%d%d, %d SMs, %.1f GB, device %d)", dev->prop.name, dev->prop.major, dev->prop.minor,
+             dev->prop.multiProcessorCount, (double)dev->prop.totalGlobalMem / 1e9, dev->ordinal);
+    return QVX_OK;
+}
+
+int32_t qvx_supports(qvx_device*, uint32_t dtype) { return dtype <= QVX_F16 ? 1 : 0; }
+
+const char* qvx_last_error(qvx_device* dev) { return dev ? dev->last_error.c_str() : g_last_error.c_str(); }
+
+uint64_t qvx_kv_pool(qvx_device* dev) { return dev ? dev->cfg.kv_pool : 0; }
+
+uint64_t qvx_max_arena(qvx_device* dev) { return dev ? (uint64_t)dev->prop.totalGlobalMem : 0; }
+
+int32_t qvx_routes_moe_attention(qvx_device* dev, size_t, size_t, size_t s) { return dev && s > 0 && s <= 65535; }
+
+int32_t qvx_alloc(qvx_device* dev, size_t len, qvx_buffer** out) {
+    if (!dev || !out) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    return new_buffer(dev, len, true, out);
+}
+
+int32_t qvx_upload(qvx_device* dev, const void* data, size_t len, qvx_buffer** out) {
+    if (!dev || !out || (!data && len)) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    int32_t rc = new_buffer(dev, len, false, out);
+    if (rc) return rc;
+    uint64_t t0 = now_ns();
+    cudaError_t e = cudaMemcpy((*out)->ptr, data, len, cudaMemcpyHostToDevice);
+    dev->xfer.transfer_ns += now_ns() - t0;
+    dev->xfer.uploads++; dev->xfer.upload_bytes += len;
+    return check_cuda(dev, e, "upload");
+}
+
+int32_t qvx_write(qvx_device* dev, qvx_buffer* buf, size_t offset, const void* data, size_t len) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    int32_t rc = buffer_of(dev, buf);
+    if (rc) return rc;
+    if (!buf->arena) return fail(dev, QVX_ERR_DEVICE, "cuda device error: only an arena (alloc) can be written");
+    if (offset > buf->len || len > buf->len - offset)
+        return fail(dev, QVX_ERR_DEVICE, "cuda device error: %zu bytes at %zu are outside a %zu-byte buffer", len, offset, buf->len);
+    cudaSetDevice(dev->ordinal);
+    uint64_t t0 = now_ns();
+    cudaError_t e = cudaMemcpy((char*)buf->ptr + offset, data, len, cudaMemcpyHostToDevice);
+    dev->xfer.transfer_ns += now_ns() - t0;
+    dev->xfer.uploads++; dev->xfer.upload_bytes += len;
+    return check_cuda(dev, e, "write");
+}
+
+int32_t qvx_read(qvx_device* dev, qvx_buffer* buf, size_t offset, void* data, size_t len) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    int32_t rc = buffer_of(dev, buf);
+    if (rc) return rc;
+    if (offset > buf->len || len > buf->len - offset)
+        return fail(dev, QVX_ERR_DEVICE, "cuda device error: %zu bytes at %zu are outside a %zu-byte buffer", len, offset, buf->len);
+    cudaSetDevice(dev->ordinal);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(data, (char*)buf->ptr + offset, len, cudaMemcpyDeviceToHost);
+    return check_cuda(dev, e, "read");
+}
+
+void qvx_retain(qvx_buffer* buf) {
+    if (!buf) return;
+    std::lock_guard<std::mutex> lk(buf->dev->mu);
+    buf->refs++;
+}
+
+void qvx_free(qvx_buffer* buf) {
+    if (!buf) return;
+    qvx_device* dev = buf->dev;
+    {
+        std::lock_guard<std::mutex> lk(dev->mu);
+        if (--buf->refs > 0) return;
+        cudaSetDevice(dev->ordinal);
+        cudaDeviceSynchronize();
+        cudaFree(buf->ptr);
+        dev->usage.used -= buf->len;
+    }
+    delete buf;
+}
+
+void* qvx_buffer_ptr(qvx_buffer* buf) { return buf ? buf->ptr : nullptr; }
+size_t qvx_buffer_len(qvx_buffer* buf) { return buf ? buf->len : 0; }
+
+int32_t qvx_get_usage(qvx_device* dev, qvx_usage* out) {
+    if (!dev || !out) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    *out = dev->usage;
+    return QVX_OK;
+}
+
+int32_t qvx_get_transfers(qvx_device* dev, qvx_transfer_stats* out) {
+    if (!dev || !out) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    drain_timers(dev);
+    *out = dev->xfer;
+    return QVX_OK;
+}
+
+int32_t qvx_get_kernel_times(qvx_device* dev, qvx_kernel_times* out) {
+    if (!dev || !out) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    drain_timers(dev);
+    *out = dev->ktimes;
+    return check_status(dev);
+}
+
+int32_t qvx_reset_kernel_times(qvx_device* dev) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    drain_timers(dev);
+    memset(&dev->ktimes, 0, sizeof dev->ktimes);
+    return QVX_OK;
+}
+
+// ---- kernels on device memory ---------------------------------------------------------------------
+int32_t qvx_kv_sync(qvx_device* dev, const qvx_geometry* geo, void* pool, size_t pool_blocks, const float* rows,
+                    const uint32_t* sync_to, size_t n, void* stream) {
+    if (!dev) return QVX_ERR_SHAPE;
+    if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
+    (void)pool_blocks;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    Layout L = make_layout(geo);
+    size_t kv_out = (size_t)L.kvh * L.d;
+    return launch_kv_rows(dev, L, pool, rows, rows + kv_out, 2 * kv_out, sync_to, nullptr, nullptr, nullptr, n,
+                          QVX_K_SYNC, (cudaStream_t)stream);
+}
+
+int32_t qvx_kv_append(qvx_device* dev, const qvx_geometry* geo, void* pool, size_t pool_blocks, const float* k_new,
+                      const float* v_new, const uint32_t* pos, const uint32_t* blocks, const uint32_t* table_at,
+                      size_t s, void* stream) {
+    if (!dev) return QVX_ERR_SHAPE;
+    if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
+    (void)pool_blocks;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    Layout L = make_layout(geo);
+    size_t kv_out = (size_t)L.kvh * L.d;
+    return launch_kv_rows(dev, L, pool, k_new, v_new, kv_out, nullptr, pos, blocks, table_at, s, QVX_K_APPEND,
+                          (cudaStream_t)stream);
+}
+
+int32_t qvx_tables_create(qvx_device* dev, const qvx_geometry* geo, size_t pool_blocks, size_t heads, size_t s,
+                          const uint32_t* pos, const uint32_t* blocks, size_t n_blocks, const uint32_t* table_at,
+                          qvx_tables** out) {
+    if (!dev || !out) return QVX_ERR_SHAPE;
+    if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    Layout L = make_layout(geo);
+    int32_t rc = validate_tables(dev, L, pool_blocks, heads, s, pos, blocks, n_blocks, table_at);
+    if (rc) return rc;
+    TableImage im = plan_image(L, heads, s, pos, n_blocks, attn_split_supported(L, heads));
+    std::vector<uint8_t> img(im.bytes);
+    fill_image(im, img.data(), L, heads, s, pos, blocks, n_blocks, table_at);
+    void* d = nullptr;
+    cudaError_t e = cudaMalloc(&d, im.bytes);
+    if (e != cudaSuccess) return check_cuda(dev, e, "tables");
+    e = cudaMemcpy(d, img.data(), im.bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(d); return check_cuda(dev, e, "tables"); }
+    qvx_tables* t = new qvx_tables;
+    t->dev = dev; t->L = L; t->pool_blocks = pool_blocks; t->heads = heads; t->s = s; t->n_blocks = n_blocks;
+    bind_image(t, im, d);
+    t->owns_dmem = true;
+    // Grow the scratch now, so a later launch never has to.
+    rc = ensure_partials(dev, attn_partial_floats(t));
+    if (rc) { cudaFree(d); delete t; return rc; }
+    *out = t;
+    return QVX_OK;
+}
+
+void qvx_tables_free(qvx_tables* t) {
+    if (!t) return;
+    if (t->owns_dmem && t->dmem) {
+        std::lock_guard<std::mutex> lk(t->dev->mu);
+        cudaSetDevice(t->dev->ordinal);
+        cudaFree(t->dmem);
+    }
+    delete t;
+}
+const uint32_t* qvx_tables_pos(qvx_tables* t) { return t ? t->d_pos : nullptr; }
+const uint32_t* qvx_tables_blocks(qvx_tables* t) { return t ? t->d_blocks : nullptr; }
+const uint32_t* qvx_tables_table_at(qvx_tables* t) { return t ? t->d_table_at : nullptr; }
+
+int32_t qvx_attn_decode(qvx_device* dev, qvx_tables* tables, const void* pool, const float* q, float* out,
+                        uint32_t variant, void* stream) {
+    if (!dev || !tables || tables->dev != dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    return run_attention(dev, tables, pool, q, out, variant, (cudaStream_t)stream);
+}
+
+int32_t qvx_block_copy(qvx_device* dev, const qvx_geometry* geo, void* pool, size_t pool_blocks, const uint32_t* src,
+                       const uint32_t* dst, size_t n, void* stream) {
+    if (!dev) return QVX_ERR_SHAPE;
+    if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
+    (void)pool_blocks;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    return launch_block_copy(dev, make_layout(geo), pool, src, dst, n, (cudaStream_t)stream);
+}
+
+// ---- the op with host memory ----------------------------------------------------------------------
+static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, size_t heads,
+                                      size_t s, const float* q, const float* k_new, const float* v_new,
+                                      const uint32_t* pos, const uint32_t* blocks, size_t n_blocks,
+                                      const uint32_t* table_at, const float* sync, const uint32_t* sync_to,
+                                      size_t n_sync, float* out, uint32_t variant) {
+    uint64_t t0 = now_ns();
+    int32_t rc = buffer_of(dev, pool);
+    if (rc) return rc;
+    if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
+    if (!pool->arena) return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: the KV pool is not an arena");
+    Layout L = make_layout(geo);
+    const size_t held = pool->len / L.block_bytes;
+    rc = validate_tables(dev, L, held, heads, s, pos, blocks, n_blocks, table_at);
+    if (rc) return rc;
+    for (size_t i = 0; i < n_sync; i++)
+        if (sync_to[i] / L.B >= held)
+            return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: a block past the pool's %zu", held);
+    if (variant == QVX_ATTN_SPLIT && !attn_split_supported(L, heads))
+        return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no split attention kernel for this geometry");
+    if (s == 0 && n_sync == 0) return QVX_OK;
+
+    const size_t kv_out = (size_t)L.kvh * L.d, q_out = heads * L.d;
+    const bool split = attn_split_supported(L, heads) && variant != QVX_ATTN_EXACT;
+    TableImage im = plan_image(L, heads, s, pos, n_blocks, split);
+    // Staged on the device for this op: the tables image, sync_to, q, k_new, v_new, sync rows, out.
+    auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t o_img = 0, o_syncto = o_img + im.bytes, o_q = o_syncto + up(4 * n_sync),
+                 o_k = o_q + up(4 * s * q_out), o_v = o_k + up(4 * s * kv_out), o_sync = o_v + up(4 * s * kv_out),
+                 o_out = o_sync + up(8 * n_sync * kv_out), total = o_out + up(4 * s * q_out);
+    if (ensure_staging(dev, total) != QVX_OK) {
+        rc = wait_locked(dev);
+        if (rc) return rc;
+        if (dev->staging_cap < total) {
+            rc = grow_staging(dev, total);
+            if (rc) return rc;
+        }
+    }
+    DeviceExtras* x = extras(dev);
+    const size_t base = dev->staging_used;
+    dev->staging_used += total;
+    uint8_t* hs = (uint8_t*)dev->staging + base;
+    uint8_t* ds = (uint8_t*)dev->dstaging + base;
+
+    fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at);
+    // A position listed twice: the later row wins (the reference writes them in list order).
+    uint32_t* st = (uint32_t*)(hs + o_syncto);
+    {
+        std::unordered_set<uint32_t> seen;
+        seen.reserve(n_sync * 2);
+        for (size_t i = n_sync; i-- > 0;) st[i] = seen.insert(sync_to[i]).second ? sync_to[i] : 0xffffffffu;
+    }
+    qvx_tables* t = new qvx_tables;
+    t->dev = dev; t->L = L; t->pool_blocks = held; t->heads = heads; t->s = s; t->n_blocks = n_blocks;
+    bind_image(t, im, ds + o_img);
+    t->owns_dmem = false;
+    dev->inflight_tables.push_back(t);
+    if (split) {
+        rc = ensure_partials(dev, attn_partial_floats(t));
+        if (rc) return rc;
+    }
+
+    cudaStream_t h2d = x->h2d, cs = dev->stream, d2h = x->d2h;
+    cudaError_t e = cudaMemcpyAsync(ds + o_img, hs + o_img, im.bytes + up(4 * n_sync), cudaMemcpyHostToDevice, h2d);
+    size_t in_bytes = im.bytes + 4 * n_sync;
+    auto copy_in = [&](size_t off, const void* src, size_t bytes) {
+        if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(ds + off, src, bytes, cudaMemcpyHostToDevice, h2d);
+        in_bytes += bytes;
+    };
+    copy_in(o_q, q, 4 * s * q_out);
+    copy_in(o_k, k_new, 4 * s * kv_out);
+    copy_in(o_v, v_new, 4 * s * kv_out);
+    copy_in(o_sync, sync, 8 * n_sync * kv_out);
+    if (e != cudaSuccess) return check_cuda(dev, e, "copy in");
+    cudaEvent_t ev_in = next_event(x);
+    cudaEventRecord(ev_in, h2d);
+    cudaStreamWaitEvent(cs, ev_in, 0);
+
+    // sync rows, then the new rows, then attention: sim.rs:385-429.
+    const float* d_sync = (const float*)(ds + o_sync);
+    rc = launch_kv_rows(dev, L, pool->ptr, d_sync, d_sync + kv_out, 2 * kv_out, (const uint32_t*)(ds + o_syncto), nullptr,
+                        nullptr, nullptr, n_sync, QVX_K_SYNC, cs);
+    if (rc == QVX_OK)
+        rc = launch_kv_rows(dev, L, pool->ptr, (const float*)(ds + o_k), (const float*)(ds + o_v), kv_out, nullptr,
+                            t->d_pos, t->d_blocks, t->d_table_at, s, QVX_K_APPEND, cs);
+    if (rc == QVX_OK && s)
+        rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), (float*)(ds + o_out), variant, cs);
+    if (rc) return rc;
+    cudaEvent_t ev_done = next_event(x);
+    cudaEventRecord(ev_done, cs);
+    cudaStreamWaitEvent(d2h, ev_done, 0);
+    if (s) {
+        e = cudaMemcpyAsync(out, ds + o_out, 4 * s * q_out, cudaMemcpyDeviceToHost, d2h);
+        if (e != cudaSuccess) return check_cuda(dev, e, "copy out");
+    }
+    // The next op's copies may overwrite nothing this op reads: each op has its own staging.
+    dev->xfer.submissions++;
+    dev->xfer.activations_in += in_bytes;
+    dev->xfer.activations_out += 4 * s * q_out;
+    dev->xfer.submit_ns += now_ns() - t0;
+    return QVX_OK;
+}
+
+int32_t qvx_paged_attention_host_async(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, size_t heads,
+                                       size_t s, const float* q, const float* k_new, const float* v_new,
+                                       const uint32_t* pos, const uint32_t* blocks, size_t n_blocks,
+                                       const uint32_t* table_at, const float* sync, const uint32_t* sync_to,
+                                       size_t n_sync, float* out, uint32_t variant) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    return paged_attention_submit(dev, pool, geo, heads, s, q, k_new, v_new, pos, blocks, n_blocks, table_at, sync,
+                                  sync_to, n_sync, out, variant);
+}
+
+int32_t qvx_wait(qvx_device* dev) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    return wait_locked(dev);
+}
+
+int32_t qvx_paged_attention_host(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, size_t heads, size_t s,
+                                 const float* q, const float* k_new, const float* v_new, const uint32_t* pos,
+                                 const uint32_t* blocks, size_t n_blocks, const uint32_t* table_at, const float* sync,
+                                 const uint32_t* sync_to, size_t n_sync, float* out, uint32_t variant) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    int32_t rc = paged_attention_submit(dev, pool, geo, heads, s, q, k_new, v_new, pos, blocks, n_blocks, table_at,
+                                        sync, sync_to, n_sync, out, variant);
+    int32_t rc2 = wait_locked(dev);
+    return rc ? rc : rc2;
+}
+
+int32_t qvx_block_copy_host(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, const uint32_t* src,
+                            const uint32_t* dst, size_t n) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    int32_t rc = buffer_of(dev, pool);
+    if (rc) return rc;
+    if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
+    if (!pool->arena) return fail(dev, QVX_ERR_SHAPE, "shape mismatch in block copy: the KV pool is not an arena");
+    Layout L = make_layout(geo);
+    const size_t held = pool->len / L.block_bytes;
+    std::unordered_set<uint32_t> dsts, srcs;
+    for (size_t i = 0; i < n; i++) {
+        if (src[i] >= held || dst[i] >= held)
+            return fail(dev, QVX_ERR_SHAPE, "shape mismatch in block copy: a block past the pool's %zu", held);
+        if (src[i] != dst[i]) { srcs.insert(src[i]); }
+    }
+    for (size_t i = 0; i < n; i++) {
+        if (src[i] == dst[i]) continue;
+        if (!dsts.insert(dst[i]).second || srcs.count(dst[i]))
+            return fail(dev, QVX_ERR_SHAPE, "shape mismatch in block copy: block %u is written twice or also read", dst[i]);
+    }
+    if (n == 0) return QVX_OK;
+    rc = wait_locked(dev);
+    if (rc) return rc;
+    uint32_t* d = nullptr;
+    cudaError_t e = cudaMalloc((void**)&d, 8 * n);
+    if (e != cudaSuccess) return check_cuda(dev, e, "block copy lists");
+    e = cudaMemcpyAsync(d, src, 4 * n, cudaMemcpyHostToDevice, dev->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d + n, dst, 4 * n, cudaMemcpyHostToDevice, dev->stream);
+    rc = e == cudaSuccess ? launch_block_copy(dev, L, pool->ptr, d, d + n, n, dev->stream) : check_cuda(dev, e, "block copy lists");
+    cudaStreamSynchronize(dev->stream);
+    cudaFree(d);
+    dev->xfer.submissions++;
+    dev->xfer.activations_in += 8 * n;
+    return rc;
+}
+
+}  // extern "C"

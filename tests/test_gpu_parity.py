@@ -1,0 +1,244 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on identical seeded inputs.
+
+Bars: pool bytes bit-exact after sync / append / copies; exact-order attention bit-exact;
+split attention within max-abs 1e-5 (f32) or 2e-3 + 1e-2 * |ref| (bf16 / f16).
+"""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import Case, XorShift, within
+from qubivex_b200 import device as qd
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_is_the_cuda_backend(dev):
+    assert dev.name() == "cuda"
+    assert "sm_100" in dev.describe() or "B200" in dev.describe()
+    assert dev.supports(qd.BF16) and dev.supports(qd.F32) and dev.supports(qd.F16)
+    assert dev.routes_moe_attention(64, 8, 1)
+
+
+# ---- sync + append: pool bytes ------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("layout,B,kvh,d", [(1, 16, 2, 64), (1, 32, 4, 128), (0, 256, 2, 32), (0, 16, 3, 24), (1, 16, 1, 256)])
+def test_sync_and_append_leave_the_oracles_bytes(dev, dtype, layout, B, kvh, d):
+    if layout == 1 and (d * (4 if dtype == "f32" else 2)) % 128:
+        pytest.skip("native rows are multiples of 128 bytes")
+    c = Case(kvh * 2, kvh, d, B, dtype, [1, B, B + 1, 3 * B - 1, 37], seed=11, layout=layout, fill=0xAB)
+    want_pool, _ = c.run_oracle()
+    got_pool, _ = c.run_device(dev, variant=qd.ATTN_EXACT)
+    assert np.array_equal(got_pool, want_pool)
+
+
+def test_a_later_duplicate_sync_row_wins(dev):
+    c = Case(4, 2, 64, 16, "bf16", [40], seed=3)
+    # The same position twice with different rows: list order decides (sim.rs:391-393).
+    c.sync_to = np.concatenate([c.sync_to, c.sync_to[5:9]])
+    extra = np.random.default_rng(5).standard_normal((4, c.sync.shape[1]), dtype=np.float32)
+    c.sync = np.concatenate([c.sync, extra])
+    want_pool, want = c.run_oracle()
+    got_pool, got = c.run_device(dev)
+    assert np.array_equal(got_pool, want_pool)
+    assert within(got, want, "bf16")[0]
+
+
+# ---- exact-order attention: bits ------------------------------------------------------------
+@pytest.mark.parametrize("layout,B,heads,kvh,d,lengths", [
+    (0, 256, 4, 2, 32, [1, 2, 250, 257, 300]),       # the reference's layout and block size, crossing a block
+    (1, 16, 8, 2, 64, [37, 128, 255, 512]),           # C1's shape
+    (0, 16, 4, 4, 16, [1, 16, 17, 100]),              # the tiny fixtures' head size
+    (1, 32, 16, 16, 128, [139]),                      # OLMoE's heads
+])
+def test_exact_attention_has_the_oracles_bits_f32(dev, layout, B, heads, kvh, d, lengths):
+    c = Case(heads, kvh, d, B, "f32", lengths, seed=21, layout=layout)
+    want_pool, want = c.run_oracle()
+    got_pool, got = c.run_device(dev, variant=qd.ATTN_EXACT)
+    assert np.array_equal(got_pool, want_pool)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_exact_attention_has_the_oracles_bits_16bit_kv(dev, dtype):
+    c = Case(8, 2, 64, 16, dtype, [1, 63, 200], seed=22)
+    _, want = c.run_oracle()
+    _, got = c.run_device(dev, variant=qd.ATTN_EXACT)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+# The reference's kernel harness: shapes, (s, p0) cases and amplitudes of
+# crates/qubivex-backend-vulkan/tests/attention_spike.rs:406-441, its xorshift generator.
+@pytest.mark.parametrize("heads,kvh,d", [(16, 16, 128), (8, 2, 64), (4, 4, 96), (2, 1, 200)])
+@pytest.mark.parametrize("amp", [1.0, 4.0, 30.0])
+def test_exact_attention_on_the_references_harness_cases(dev, heads, kvh, d, amp):
+    for p0 in (0, 1, 63, 64, 137, 1000):
+        n = p0 + 1
+        r = XorShift(7 + p0)
+        q = r.uni(amp, heads * d).reshape(1, heads, d)
+        k = r.uni(amp, n * kvh * d).reshape(n, kvh * d)
+        v = r.uni(1.0, n * kvh * d).reshape(n, kvh * d)
+        native_ok = (d * 4) % 128 == 0
+        c = Case(heads, kvh, d, 16, "f32", [n], seed=1, layout=1 if native_ok else 0)
+        c.q, c.k_new, c.v_new = q, k[-1:].copy(), v[-1:].copy()
+        c.sync = np.concatenate([k[:-1], v[:-1]], axis=1).astype(np.float32)
+        _, want = c.run_oracle()
+        _, got = c.run_device(dev, variant=qd.ATTN_EXACT)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (heads, kvh, d, amp, p0)
+        if native_ok and d in (64, 128):
+            _, fast = c.run_device(dev, variant=qd.ATTN_SPLIT)
+            ok, err = within(fast, want, "f32")
+            # amplitude 30 makes scores of +-1e3: the tolerance is for N(0,1)-scale inputs
+            assert ok or amp > 4.0, (heads, kvh, d, amp, p0, err)
+            assert np.all(np.isfinite(fast))
+
+
+def test_nan_and_inf_keys_follow_the_reference(dev):
+    # attention_spike.rs feeds NaN / Inf keys: the maximum ignores NaN, the sum does not.
+    c = Case(4, 2, 64, 16, "f32", [50], seed=9)
+    c.sync[7, :64] = np.nan
+    c.sync[9, 3] = np.inf
+    _, want = c.run_oracle()
+    _, got = c.run_device(dev, variant=qd.ATTN_EXACT)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    m = ~np.isnan(want)
+    assert np.array_equal(got[m].view(np.uint32), want[m].view(np.uint32))
+
+
+# ---- split attention: tolerance ---------------------------------------------------------------
+@pytest.mark.parametrize("dtype,heads,kvh,d,B", [
+    ("f32", 8, 2, 64, 16), ("f32", 4, 4, 128, 16), ("f32", 16, 2, 64, 32), ("f32", 2, 1, 64, 16),
+    ("bf16", 32, 4, 128, 16), ("bf16", 32, 8, 128, 32), ("bf16", 8, 8, 64, 16), ("bf16", 24, 2, 128, 16),
+    ("bf16", 8, 1, 256, 16), ("f16", 32, 4, 128, 16), ("f16", 4, 2, 64, 64), ("bf16", 64, 8, 128, 256),
+])
+def test_split_attention_is_within_tolerance(dev, dtype, heads, kvh, d, B):
+    lengths = [1, 2, 15, 16, 17, 255, 256, 257, 511, 700, 1023, 1500]
+    c = Case(heads, kvh, d, B, dtype, lengths, seed=31, fill=0xFF)  # 0xFF bytes are NaNs: tails must be masked
+    want_pool, want = c.run_oracle()
+    got_pool, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
+    assert np.array_equal(got_pool, want_pool)
+    ok, err = within(got, want, dtype)
+    assert ok, f"max abs err {err}"
+    assert np.all(np.isfinite(got))
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_split_attention_with_scaled_inputs(dev, dtype):
+    # The benchmark's distribution: values ~ N(0,1) / sqrt(d); outputs are small, so check
+    # the relative error directly as well.
+    d = 128
+    c = Case(32, 4, d, 16, dtype, [1024, 2048, 3000, 4096], seed=41, amp_qk=d ** -0.5, amp_v=d ** -0.5)
+    _, want = c.run_oracle()
+    _, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
+    ok, err = within(got, want, dtype)
+    assert ok, err
+    scale = float(np.abs(want).max())
+    assert err <= (1e-5 if dtype == "f32" else 2e-2 * scale)
+
+
+def test_a_sequences_result_does_not_depend_on_its_batch(dev):
+    # ADR-017 (docs/decisions/ADR-017-BATCHING.md:248-256): batch invariance, bit for bit.
+    full = Case(32, 4, 128, 16, "bf16", [900, 300, 2047, 33, 1200], seed=51)
+    _, out_full = full.run_device(dev, variant=qd.ATTN_SPLIT)
+    for t in (0, 2, 3):
+        alone = Case(32, 4, 128, 16, "bf16", [int(full.lengths[t])], seed=52, pool_blocks=full.pool_blocks)
+        # the same sequence: same blocks, rows and query, alone in its op
+        nb = (int(full.lengths[t]) + 15) // 16
+        alone.blocks = full.blocks[full.table_at[t]:full.table_at[t] + nb].copy()
+        alone.table_at[:] = 0
+        alone.q, alone.k_new, alone.v_new = full.q[t:t + 1], full.k_new[t:t + 1], full.v_new[t:t + 1]
+        lo = int(sum(int(x) - 1 for x in full.lengths[:t]))
+        alone.sync = full.sync[lo:lo + int(full.lengths[t]) - 1]
+        alone.sync_to = full.sync_to[lo:lo + int(full.lengths[t]) - 1]
+        _, out_alone = alone.run_device(dev, variant=qd.ATTN_SPLIT)
+        assert np.array_equal(out_alone[0].view(np.uint32), out_full[t].view(np.uint32))
+
+
+# ---- validation: nothing written on a shape error (sim.rs:313-324, :359-376) ---------------------
+def test_bad_inputs_are_refused_before_anything_is_written(dev):
+    c = Case(8, 2, 64, 16, "f32", [20, 40], seed=61)
+    buf = dev.alloc(c.pool_blocks * c.bb)
+    zeros = c.host_pool()
+    dev.write(buf, 0, zeros)
+    args = lambda **kw: dict(dict(pool=buf, geo=c.geo_d, heads=c.heads, q=c.q, k_new=c.k_new, v_new=c.v_new,
+                                  pos=c.pos, blocks=c.blocks, table_at=c.table_at, sync=c.sync, sync_to=c.sync_to), **kw)
+    bad_blocks = c.blocks.copy(); bad_blocks[1] = c.pool_blocks
+    with pytest.raises(qd.ShapeError):
+        dev.paged_attention(**args(blocks=bad_blocks))                       # a block past the pool
+    bad_sync = c.sync_to.copy(); bad_sync[0] = c.pool_blocks * 16
+    with pytest.raises(qd.ShapeError):
+        dev.paged_attention(**args(sync_to=bad_sync))                        # a sync row past the pool
+    with pytest.raises(qd.ShapeError):
+        dev.paged_attention(**args(pos=np.array([20, 400], dtype=np.uint32)))  # no block for the position
+    with pytest.raises(qd.ShapeError):
+        dev.paged_attention(**args(heads=7, q=c.q[:, :7].copy()))            # heads % kv_heads
+    with pytest.raises(qd.ShapeError):
+        dev.paged_attention(**args(k_new=c.k_new[:1]))                       # a short k_new
+    fixed = dev.upload(zeros)
+    with pytest.raises(qd.ShapeError):
+        dev.paged_attention(**args(pool=fixed))                              # the pool is not an arena
+    with pytest.raises(qd.DeviceError):
+        dev.write(fixed, 0, zeros[:16])                                      # only an arena can be written
+    with pytest.raises(qd.DeviceError):
+        dev.write(buf, len(zeros) - 8, zeros[:16])                           # outside the buffer
+    with pytest.raises(qd.Unsupported):
+        dev.paged_attention(**args(geo=qd.geometry(16, 2, 16, qd.F32, qd.LAYOUT_NATIVE)))
+    assert np.array_equal(dev.read(buf, 0, len(zeros)), zeros)
+    fixed.free()
+    buf.free()
+
+
+def test_capacity_is_enforced_and_freed(dev):
+    # crates/qubivex-backend-cpu/src/sim.rs:721-876: capacity enforced, freed on drop, refusals counted.
+    from qubivex_b200.device import CudaDevice
+    small = CudaDevice(0, capacity=1 << 20)
+    a = small.alloc(600_000)
+    with pytest.raises(qd.OutOfDeviceMemory):
+        small.alloc(600_000)
+    u = small.usage()
+    assert (u.capacity, u.used, u.refused) == (1 << 20, 600_000, 1)
+    a.free()
+    b = small.alloc(1 << 20)
+    assert small.usage().used == 1 << 20 and small.usage().peak == 1 << 20
+    b.free()
+    assert small.usage().used == 0
+    small.close()
+
+
+# ---- block copies -------------------------------------------------------------------------------
+@pytest.mark.parametrize("B,kvh,d,dtype,layout", [(16, 4, 128, "bf16", 1), (32, 8, 128, "bf16", 1), (3, 1, 5, "f32", 0)])
+def test_block_copies_move_the_oracles_bytes(dev, B, kvh, d, dtype, layout):
+    geo_o = oracle.geometry(B, kvh, d, {"f32": 0, "bf16": 1}[dtype], layout)
+    geo_d = qd.geometry(B, kvh, d, {"f32": 0, "bf16": 1}[dtype], layout)
+    n = 64
+    bb = oracle.block_bytes(geo_o)
+    rng = np.random.default_rng(71)
+    host = rng.integers(0, 256, size=n * bb, dtype=np.uint8)
+    perm = rng.permutation(n).astype(np.uint32)
+    src, dst = perm[:20], perm[20:40]
+    src = np.concatenate([src, [perm[41]]]).astype(np.uint32)  # a move onto itself is a no-op
+    dst = np.concatenate([dst, [perm[41]]]).astype(np.uint32)
+    want = host.copy()
+    assert oracle.block_copy(want, geo_o, src, dst) == 0
+    buf = dev.alloc(n * bb)
+    dev.write(buf, 0, host)
+    dev.block_copy(buf, geo_d, src, dst)
+    assert np.array_equal(dev.read(buf, 0, n * bb), want)
+    with pytest.raises(qd.ShapeError):
+        dev.block_copy(buf, geo_d, [0, 1], [2, 2])      # written twice
+    with pytest.raises(qd.ShapeError):
+        dev.block_copy(buf, geo_d, [0, 1], [1, 2])      # read and written
+    with pytest.raises(qd.ShapeError):
+        dev.block_copy(buf, geo_d, [0], [n])            # past the pool
+    buf.free()
+
+
+def test_kernel_times_are_counted(dev):
+    dev.reset_kernel_times()
+    c = Case(32, 4, 128, 16, "bf16", [600, 100], seed=81)
+    c.run_device(dev, variant=qd.ATTN_SPLIT)
+    kt = dev.kernel_times()
+    assert kt["sync"][0] == 1 and kt["append"][0] == 1 and kt["attn"][0] == 1 and kt["reduce"][0] == 1
+    assert kt["attn"][1] > 0
+    t = dev.transfers()
+    assert t.submissions >= 1 and t.activations_out >= c.q.nbytes and t.timed >= 4
