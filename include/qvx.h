@@ -118,7 +118,7 @@ int32_t qvx_get_transfers(qvx_device *dev, qvx_transfer_stats *out);
 #define QVX_K_SYNC 0
 #define QVX_K_APPEND 1
 #define QVX_K_ATTN 2     /* the split decode-attention kernel                              */
-#define QVX_K_REDUCE 3   /* the merge of its partial results                               */
+#define QVX_K_REDUCE 3   /* unused: the split kernel merges its own partial results         */
 #define QVX_K_EXACT 4    /* the reference-order decode-attention kernel                    */
 #define QVX_K_COPY 5     /* block copies (copy-on-write, compaction)                       */
 #define QVX_K_COUNT 6

@@ -1,5 +1,6 @@
 // Paged decode attention, the fast path: GQA-grouped, online (flash-style) softmax, split
-// over the context, with a second kernel that merges the splits in a fixed order.
+// over the context; the CTA that finishes a sequence's last split merges all of them, in
+// split order, so the sum order is fixed whichever CTA does it.
 //
 // Computes what `attn_decode.comp` (crates/qubivex-backend-vulkan/shaders/attn_decode.comp:60-175)
 // and the gather + `attend` of the CPU device (crates/qubivex-backend-cpu/src/sim.rs:400-429,
@@ -117,6 +118,24 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
         return *reinterpret_cast<uint32_t*>(&v);
     }
 }
+// x = hi + lo with hi the nearest 16-bit value and lo the rounded remainder: two tensor-core
+// passes then carry ~16 bits of mantissa instead of 8 (bf16) or 11 (f16).
+template <int DT>
+__device__ __forceinline__ void split16(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    if constexpr (DT == QVX_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+        float2 hf = __bfloat1622float2(h);
+        __nv_bfloat162 l = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
+        hi = *reinterpret_cast<uint32_t*>(&h);
+        lo = *reinterpret_cast<uint32_t*>(&l);
+    } else {
+        __half2 h = __floats2half2_rn(x0, x1);
+        float2 hf = __half22float2(h);
+        __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+        hi = *reinterpret_cast<uint32_t*>(&h);
+        lo = *reinterpret_cast<uint32_t*>(&l);
+    }
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -129,13 +148,24 @@ struct SplitArgs {
     const float* q;             // [token][head][d]
     float* out;                 // [token][head][d]
     float* partials;            // n_parts x (8*d + 16): acc[8][d], m[8], l[8]
-    const qvx_item* items;
-    const uint32_t* blocks;
+    uint32_t* counters;         // one per split (sequence, group): arrivals so far; zero between launches
+    const uint32_t* items;      // n_items x item_words: header, then the item's block ids
     int* status;                // a kernel that gave up a wait leaves a code here
     uint64_t block_bytes;
-    uint32_t page_bytes, row_bytes, tiles_per_block, heads, d;
+    uint32_t page_bytes, row_bytes, tiles_per_block, heads, d, item_words;
     float scale_log2;           // (1 / sqrt(d)) * log2(e)
 };
+
+struct Item {
+    uint32_t seq, tokens, head0, nheads, kv_head, part, part0, nch, counter;
+};
+__device__ __forceinline__ Item load_item(const uint32_t* w) {
+    uint4 a = *reinterpret_cast<const uint4*>(w), b = *reinterpret_cast<const uint4*>(w + 4);
+    Item it;
+    it.seq = a.x; it.tokens = a.y; it.head0 = a.z; it.nheads = a.w & 0xffffu; it.kv_head = a.w >> 16;
+    it.part = b.x; it.part0 = b.y; it.nch = b.z; it.counter = b.w;
+    return it;
+}
 
 // Shared memory per CTA: WARPS rings of `stages` stages (a stage = a key tile then a value
 // tile, 16 rows each), the f32 path's query and probability scratch, the mbarriers.  After
@@ -186,9 +216,11 @@ struct TileStream {
 };
 
 // Merges the four warps' results (left in shared memory) and writes either the final output
-// (a sequence that fits one item) or this item's partial result.
-__device__ __forceinline__ void merge_and_store(const SplitArgs& a, const qvx_item& it, const float* res,
-                                                uint32_t res_stride_f, uint32_t d) {
+// (a sequence that fits one item) or this item's partial result.  The CTA that delivers the
+// last partial of a (sequence, group) then merges all of them in chunk order: nobody waits,
+// the arrival counter only tells the last one that it is the last.
+__device__ __forceinline__ void merge_and_store(const SplitArgs& a, const Item& it, const float* res,
+                                                uint32_t res_stride_f, uint32_t d, float* scratch) {
     // res + w * res_stride_f: m[8], l[8], acc[8][d]
     for (uint32_t i = threadIdx.x; i < it.nheads * d; i += THREADS) {
         uint32_t h = i / d, x = i % d;
@@ -211,16 +243,81 @@ __device__ __forceinline__ void merge_and_store(const SplitArgs& a, const qvx_it
             if (x == 0) { p[8 * d + h] = M; p[8 * d + 8 + h] = l; }
         }
     }
+    if (it.part == NO_PART) return;
+    __shared__ uint32_t s_last;
+    __threadfence();  // this thread's partial is visible device-wide before the arrival is counted
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(a.counters + it.counter, 1u) == it.nch - 1 ? 1u : 0u;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // The merge is latency bound (a few KiB from L2), so it is arranged as two rounds of
+    // independent loads: every chunk's (m, l) into shared memory, then the weighted sums with
+    // 16-byte loads, eight chunks in flight per thread.
+    const uint32_t stride = 8 * d + 16, nch = it.nch;
+    const float* p0 = a.partials + (size_t)it.part0 * stride;
+    float* msm = scratch;             // [nch][8] maxima, then weights
+    float* lsm = scratch + nch * 8;   // [nch][8] row sums
+    float* Lsm = lsm + nch * 8;       // [8]
+    for (uint32_t i = threadIdx.x; i < nch * 16; i += THREADS) {
+        uint32_t c = i >> 4, j = i & 15;
+        float v = __ldcg(p0 + (size_t)c * stride + 8 * d + j);
+        if (j < 8) msm[c * 8 + j] = v; else lsm[c * 8 + j - 8] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        const uint32_t h = threadIdx.x;
+        float M = -INFINITY, L = 0.f;
+        for (uint32_t c = 0; c < nch; c++) M = fmaxf(M, msm[c * 8 + h]);
+        for (uint32_t c = 0; c < nch; c++) {
+            float w = ex2(msm[c * 8 + h] - M);
+            msm[c * 8 + h] = w;
+            L = fmaf(lsm[c * 8 + h], w, L);
+        }
+        Lsm[h] = L;
+    }
+    __syncthreads();
+    const uint32_t d4 = d >> 2;
+    for (uint32_t i = threadIdx.x; i < it.nheads * d4; i += THREADS) {
+        const uint32_t h = i / d4, x = (i % d4) * 4;
+        const float* p = p0 + h * d + x;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        uint32_t c = 0;
+        for (; c + 8 <= nch; c += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(p + (size_t)(c + u) * stride));
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                float w = msm[(c + u) * 8 + h];
+                acc.x = fmaf(v[u].x, w, acc.x); acc.y = fmaf(v[u].y, w, acc.y);
+                acc.z = fmaf(v[u].z, w, acc.z); acc.w = fmaf(v[u].w, w, acc.w);
+            }
+        }
+        for (; c < nch; c++) {
+            float4 v = __ldcg(reinterpret_cast<const float4*>(p + (size_t)c * stride));
+            float w = msm[c * 8 + h];
+            acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);
+            acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
+        }
+        const float L = Lsm[h];
+        float4 o = make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
+        *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0 + h) * d + x) = o;
+    }
+    if (threadIdx.x == 0) a.counters[it.counter] = 0;  // ready for the next launch
 }
 
 // ---- 16-bit pools: tensor-core path ------------------------------------------------------
-template <int DT, int D>
+// PRECISE: queries and probabilities go through the tensor cores as value + remainder (two
+// passes); needed for bf16's 8-bit mantissa to stay inside the tolerance, not for f16's 11.
+template <int DT, int D, bool PRECISE>
 __global__ void __launch_bounds__(THREADS, 3) attn_split_mma_kernel(SplitArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     const SmemPlan sp = smem_plan(D * 2, D, false);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t g = lane >> 2, t = lane & 3;
-    const qvx_item it = a.items[blockIdx.x];
+    const uint32_t* itw = a.items + (size_t)blockIdx.x * a.item_words;
+    const Item it = load_item(itw);
     const uint32_t smem_base = smem_u32(smem);
 
     TileStream ts;
@@ -241,12 +338,13 @@ __global__ void __launch_bounds__(THREADS, 3) attn_split_mma_kernel(SplitArgs a)
     const uint32_t ntiles = (it.tokens + TILE - 1) / TILE;
     const uint32_t n_my = ntiles > warp ? (ntiles - warp + WARPS - 1) / WARPS : 0;
     ts.my_block = 0;
-    if (lane < n_my) ts.my_block = a.blocks[it.first + (warp + WARPS * lane) / a.tiles_per_block];
+    if (lane < n_my) ts.my_block = itw[QVX_ITEM_HEADER_WORDS + (warp + WARPS * lane) / a.tiles_per_block];
     const uint32_t pre = n_my < sp.stages ? n_my : sp.stages;
     for (uint32_t i = 0; i < pre; i++) ts.issue(i);
 
-    // Q^T fragments (the B operand): this lane holds head g, dims 16*ks + 2t + {0,1,8,9}.
-    uint32_t qf[D / 16][2];
+    // Q^T fragments (the B operand): this lane holds head g, dims 16*ks + 2t + {0,1,8,9}, as a
+    // 16-bit value plus a 16-bit remainder.
+    uint32_t qf[D / 16][2], ql[D / 16][2];
     {
         const bool live = g < it.nheads;
         const float* qp = a.q + ((size_t)it.seq * a.heads + it.head0 + (live ? g : 0)) * D;
@@ -257,8 +355,8 @@ __global__ void __launch_bounds__(THREADS, 3) attn_split_mma_kernel(SplitArgs a)
                 x0 = *reinterpret_cast<const float2*>(qp + 16 * ks + 2 * t);
                 x1 = *reinterpret_cast<const float2*>(qp + 16 * ks + 2 * t + 8);
             }
-            qf[ks][0] = pack16<DT>(x0.x, x0.y);
-            qf[ks][1] = pack16<DT>(x1.x, x1.y);
+            split16<DT>(x0.x, x0.y, qf[ks][0], ql[ks][0]);
+            split16<DT>(x1.x, x1.y, qf[ks][1], ql[ks][1]);
         }
     }
 
@@ -287,6 +385,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_split_mma_kernel(SplitArgs a)
             uint32_t af[4];
             ldmatrix_x4(kt + k_row * (D * 2) + (((2 * ks + k_chunk) ^ (k_row & 7)) << 4), af);
             mma_16816<DT>(sc, af, qf[ks][0], qf[ks][1]);
+            if constexpr (PRECISE) mma_16816<DT>(sc, af, ql[ks][0], ql[ks][1]);
         }
         if (valid < TILE) {
             // The tail of the last block: unwritten slots hold whatever the pool held before.
@@ -312,9 +411,13 @@ __global__ void __launch_bounds__(THREADS, 3) attn_split_mma_kernel(SplitArgs a)
         const float p2 = ex2(fmaf(sc[2], a.scale_log2, -mn0)), p3 = ex2(fmaf(sc[3], a.scale_log2, -mn1));
         l0 = fmaf(l0, al0, p0 + p2);
         l1 = fmaf(l1, al1, p1 + p3);
-        // P^T as the B operand: (position g; heads 2t,2t+1) -> (head g; positions 2t,2t+1).
-        const uint32_t pb0 = movmatrix_trans(pack16<DT>(p0, p1));
-        const uint32_t pb1 = movmatrix_trans(pack16<DT>(p2, p3));
+        // P^T as the B operand: (position g; heads 2t,2t+1) -> (head g; positions 2t,2t+1),
+        // again as value + remainder.
+        uint32_t ph0, pl0, ph1, pl1;
+        split16<DT>(p0, p1, ph0, pl0);
+        split16<DT>(p2, p3, ph1, pl1);
+        const uint32_t pb0 = movmatrix_trans(ph0), pb1 = movmatrix_trans(ph1);
+        const uint32_t pc0 = movmatrix_trans(pl0), pc1 = movmatrix_trans(pl1);
         // O^T = O^T * alpha + V^T P^T
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
@@ -322,6 +425,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_split_mma_kernel(SplitArgs a)
             uint32_t vf[4];
             ldmatrix_x4_trans(vt + v_row * (D * 2) + (((2 * mt + v_chunk) ^ (v_row & 7)) << 4), vf);
             mma_16816<DT>(o[mt], vf, pb0, pb1);
+            if constexpr (PRECISE) mma_16816<DT>(o[mt], vf, pc0, pc1);
         }
         __syncwarp();  // every lane is done reading this stage
         if (i + sp.stages < n_my) ts.issue(i + sp.stages);
@@ -356,7 +460,7 @@ __global__ void __launch_bounds__(THREADS, 3) attn_split_mma_kernel(SplitArgs a)
         res[16 + (2 * t + 1) * D + 16 * mt + g + 8] = o[mt][3];
     }
     __syncthreads();
-    merge_and_store(a, it, reinterpret_cast<const float*>(smem), res_stride_f, D);
+    merge_and_store(a, it, reinterpret_cast<const float*>(smem), res_stride_f, D, reinterpret_cast<float*>(smem));
 }
 
 // ---- f32 pools: CUDA-core path -------------------------------------------------------------
@@ -369,7 +473,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
     constexpr int DK = D / 32;   // output dims per lane
     const SmemPlan sp = smem_plan(D * 4, D, true);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const qvx_item it = a.items[blockIdx.x];
+    const uint32_t* itw = a.items + (size_t)blockIdx.x * a.item_words;
+    const Item it = load_item(itw);
     const uint32_t smem_base = smem_u32(smem);
 
     TileStream ts;
@@ -388,7 +493,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
     const uint32_t ntiles = (it.tokens + TILE - 1) / TILE;
     const uint32_t n_my = ntiles > warp ? (ntiles - warp + WARPS - 1) / WARPS : 0;
     ts.my_block = 0;
-    if (lane < n_my) ts.my_block = a.blocks[it.first + (warp + WARPS * lane) / a.tiles_per_block];
+    if (lane < n_my) ts.my_block = itw[QVX_ITEM_HEADER_WORDS + (warp + WARPS * lane) / a.tiles_per_block];
     const uint32_t pre = n_my < sp.stages ? n_my : sp.stages;
     for (uint32_t i = 0; i < pre; i++) ts.issue(i);
 
@@ -519,44 +624,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
         for (int k = 0; k < DK; k++) res[16 + h * D + lane + 32 * k] = o[h][k];
     }
     __syncthreads();
-    merge_and_store(a, it, reinterpret_cast<const float*>(smem), res_stride_f, D);
-}
-
-// ---- the merge of the splits ---------------------------------------------------------------
-// One CTA per (group, sequence) whose context was split: partials in chunk order, so the sum
-// order is fixed.  Reads n_chunks * (8*d + 16) floats, writes nheads * d.
-struct ReduceArgs {
-    const float* partials;
-    float* out;
-    const uint32_t* part_at;   // per sequence: first partial, or NO_PART when it was not split
-    const uint32_t* pos;
-    uint32_t heads, d, group_heads, groups_per_kv, chunk_tokens, ngroups;
-};
-
-__global__ void __launch_bounds__(128) attn_reduce_kernel(ReduceArgs a) {
-    const uint32_t seq = blockIdx.y, grp = blockIdx.x;
-    const uint32_t base = a.part_at[seq];
-    if (base == NO_PART) return;
-    const uint32_t n = a.pos[seq] + 1u;
-    const uint32_t nch = (n + a.chunk_tokens - 1) / a.chunk_tokens;
-    const uint32_t kv_head = grp / a.groups_per_kv, sub = grp % a.groups_per_kv;
-    const uint32_t head0 = kv_head * a.group_heads + sub * 8;
-    const uint32_t nheads = min(8u, a.group_heads - sub * 8);
-    const uint32_t d = a.d, stride = 8 * d + 16;
-    const float* p0 = a.partials + (size_t)(base + grp * nch) * stride;
-    for (uint32_t i = threadIdx.x; i < nheads * d; i += blockDim.x) {
-        uint32_t h = i / d, x = i % d;
-        float M = -INFINITY;
-        for (uint32_t c = 0; c < nch; c++) M = fmaxf(M, p0[(size_t)c * stride + 8 * d + h]);
-        float acc = 0.f, l = 0.f;
-        for (uint32_t c = 0; c < nch; c++) {
-            const float* p = p0 + (size_t)c * stride;
-            float w = ex2(p[8 * d + h] - M);
-            acc = fmaf(p[h * d + x], w, acc);
-            l = fmaf(p[8 * d + 8 + h], w, l);
-        }
-        a.out[((size_t)seq * a.heads + head0 + h) * d + x] = acc / l;
-    }
+    merge_and_store(a, it, reinterpret_cast<const float*>(smem), res_stride_f, D, reinterpret_cast<float*>(smem));
 }
 
 // ---- host side -------------------------------------------------------------------------------
@@ -573,8 +641,12 @@ size_t attn_partial_floats(const qvx_tables* t) { return t->n_parts * (size_t)(8
 template <typename K>
 static int32_t launch_one(qvx_device* dev, K kernel, const SplitArgs& a, unsigned grid, uint32_t smem,
                           cudaStream_t s) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return check_cuda(dev, e, "split attention shared memory");
+    static thread_local K configured = nullptr;  // one opt-in per kernel instantiation and thread
+    if (configured != kernel) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return check_cuda(dev, e, "split attention shared memory");
+        configured = kernel;
+    }
     kernel<<<grid, THREADS, smem, s>>>(a);
     return check_cuda(dev, cudaGetLastError(), "split attention launch");
 }
@@ -582,51 +654,40 @@ static int32_t launch_one(qvx_device* dev, K kernel, const SplitArgs& a, unsigne
 extern int* device_status_word(qvx_device* dev);
 
 int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                          float* partials, cudaStream_t s) {
+                          float* partials, uint32_t* counters, cudaStream_t s) {
     if (t->n_items == 0) return QVX_OK;
     const Layout& L = t->L;
     SplitArgs a;
-    a.pool = (const uint8_t*)pool; a.q = q; a.out = out; a.partials = partials;
-    a.items = t->d_items; a.blocks = t->d_blocks; a.status = device_status_word(dev);
+    a.pool = (const uint8_t*)pool; a.q = q; a.out = out; a.partials = partials; a.counters = counters;
+    a.items = t->d_items; a.status = device_status_word(dev);
     a.block_bytes = L.block_bytes; a.page_bytes = L.page_bytes; a.row_bytes = L.row_bytes;
-    a.tiles_per_block = L.B / TILE; a.heads = (uint32_t)t->heads; a.d = L.d;
+    a.tiles_per_block = L.B / TILE; a.heads = (uint32_t)t->heads; a.d = L.d; a.item_words = t->item_words;
     a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;
     const bool f32 = L.dtype == QVX_F32;
     const SmemPlan sp = smem_plan(L.row_bytes, L.d, f32);
     const unsigned grid = (unsigned)t->n_items;
     const size_t group = t->heads / L.kvh;
     int32_t rc = QVX_ERR_UNSUPPORTED;
-    {
-        LaunchTimer timer(dev, QVX_K_ATTN, s);
-        if (f32) {
-            const int nh = group >= 8 ? 8 : (group > 2 ? 4 : 2);
+    LaunchTimer timer(dev, QVX_K_ATTN, s);
+    if (f32) {
+        const int nh = group >= 8 ? 8 : (group > 2 ? 4 : 2);
 #define QVX_F32_CASE(DD, NN) \
     if (L.d == DD && nh == NN) rc = launch_one(dev, attn_split_f32_kernel<DD, NN>, a, grid, sp.total, s);
-            QVX_F32_CASE(64, 2) QVX_F32_CASE(64, 4) QVX_F32_CASE(64, 8)
-            QVX_F32_CASE(128, 2) QVX_F32_CASE(128, 4) QVX_F32_CASE(128, 8)
+        QVX_F32_CASE(64, 2) QVX_F32_CASE(64, 4) QVX_F32_CASE(64, 8)
+        QVX_F32_CASE(128, 2) QVX_F32_CASE(128, 4) QVX_F32_CASE(128, 8)
 #undef QVX_F32_CASE
-        } else {
-#define QVX_MMA_CASE(TT, DD) \
-    if (L.dtype == TT && L.d == DD) rc = launch_one(dev, attn_split_mma_kernel<TT, DD>, a, grid, sp.total, s);
-            QVX_MMA_CASE(QVX_BF16, 64) QVX_MMA_CASE(QVX_BF16, 128) QVX_MMA_CASE(QVX_BF16, 256)
-            QVX_MMA_CASE(QVX_F16, 64) QVX_MMA_CASE(QVX_F16, 128) QVX_MMA_CASE(QVX_F16, 256)
+    } else {
+        static const bool one_pass = getenv("QVX_ATTN_ONE_PASS") != nullptr;  // experiments only
+        const bool precise = L.dtype == QVX_BF16 && !one_pass;
+#define QVX_MMA_CASE(TT, DD, PP) \
+    if (L.dtype == TT && L.d == DD && precise == PP) \
+        rc = launch_one(dev, attn_split_mma_kernel<TT, DD, PP>, a, grid, sp.total, s);
+        QVX_MMA_CASE(QVX_BF16, 64, true) QVX_MMA_CASE(QVX_BF16, 128, true) QVX_MMA_CASE(QVX_BF16, 256, true)
+        QVX_MMA_CASE(QVX_BF16, 128, false)
+        QVX_MMA_CASE(QVX_F16, 64, false) QVX_MMA_CASE(QVX_F16, 128, false) QVX_MMA_CASE(QVX_F16, 256, false)
 #undef QVX_MMA_CASE
-        }
     }
     if (rc == QVX_ERR_UNSUPPORTED) return fail(dev, rc, "split attention: no kernel for this geometry");
-    if (rc != QVX_OK) return rc;
-    if (t->n_parts) {
-        ReduceArgs r;
-        r.partials = partials; r.out = out; r.part_at = t->d_part_at; r.pos = t->d_pos;
-        r.heads = (uint32_t)t->heads; r.d = L.d; r.group_heads = (uint32_t)group;
-        r.groups_per_kv = (uint32_t)((group + 7) / 8);
-        r.chunk_tokens = t->chunk_blocks * L.B;
-        r.ngroups = L.kvh * r.groups_per_kv;
-        LaunchTimer timer(dev, QVX_K_REDUCE, s);
-        dim3 grid2(r.ngroups, (unsigned)t->s);
-        attn_reduce_kernel<<<grid2, 128, 0, s>>>(r);
-        rc = check_cuda(dev, cudaGetLastError(), "attention reduce launch");
-    }
     return rc;
 }
 

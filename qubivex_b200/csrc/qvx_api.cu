@@ -98,6 +98,10 @@ static int32_t check_status(qvx_device* dev) {
     int st = *(volatile int*)x->status_host;
     if (st == 0) return QVX_OK;
     *(volatile int*)x->status_host = 0;
+    if (dev->counters) {  // an item that gave up never arrived: start the counters from zero again
+        cudaDeviceSynchronize();
+        cudaMemset(dev->counters, 0, dev->counters_cap * 4);
+    }
     return fail(dev, QVX_ERR_DEVICE, "cuda device error: a kernel gave up a bounded wait (status %d); its outputs are not valid", st);
 }
 
@@ -192,10 +196,19 @@ static uint32_t chunk_tokens_for(const Layout& L) {
     return c;
 }
 
+// The CTA that merges a sequence's splits keeps every split's maximum and row sum in shared
+// memory: 64 bytes per split of the 64 KiB a CTA always has.
+constexpr size_t MAX_CHUNKS = 1000;
+static int32_t too_many_chunks(qvx_device* dev, size_t nch) {
+    return fail(dev, QVX_ERR_UNSUPPORTED,
+                "cuda backend splits a context into at most %zu chunks, this one needs %zu: raise QVX_CHUNK_TOKENS",
+                MAX_CHUNKS, nch);
+}
+
 struct TableImage {
-    size_t off_pos, off_table_at, off_blocks, off_part_at, off_items, bytes;
-    size_t n_items, n_parts;
-    uint32_t max_pos, chunk_blocks;
+    size_t off_pos, off_table_at, off_blocks, off_items, bytes;
+    size_t n_items, n_parts, n_counters, max_nch;
+    uint32_t max_pos, chunk_blocks, item_words;
 };
 
 static int32_t validate_tables(qvx_device* dev, const Layout& L, size_t pool_blocks, size_t heads, size_t s,
@@ -221,21 +234,22 @@ static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint
     TableImage im{};
     uint32_t chunk = chunk_tokens_for(L);
     im.chunk_blocks = chunk / L.B;
+    im.item_words = (QVX_ITEM_HEADER_WORDS + im.chunk_blocks + 3u) & ~3u;
     size_t group = heads / L.kvh, groups = L.kvh * ((group + 7) / 8);
     for (size_t t = 0; t < s; t++) {
         im.max_pos = std::max(im.max_pos, pos[t]);
         if (!split) continue;
         size_t nch = ((size_t)pos[t] + chunk) / chunk;
+        im.max_nch = std::max<size_t>(im.max_nch, nch);
         im.n_items += nch * groups;
-        if (nch > 1) im.n_parts += nch * groups;
+        if (nch > 1) { im.n_parts += nch * groups; im.n_counters += groups; }
     }
     size_t off = 0;
     im.off_pos = off; off += 4 * s;
     im.off_table_at = off; off += 4 * s;
     im.off_blocks = off; off += 4 * n_blocks;
-    im.off_part_at = off; off += 4 * s;
     off = (off + 15) & ~(size_t)15;
-    im.off_items = off; off += sizeof(qvx_item) * im.n_items;
+    im.off_items = off; off += 4ull * im.item_words * im.n_items;
     im.bytes = (off + 255) & ~(size_t)255;
     return im;
 }
@@ -245,38 +259,44 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     memcpy(img + im.off_pos, pos, 4 * s);
     memcpy(img + im.off_table_at, table_at, 4 * s);
     memcpy(img + im.off_blocks, blocks, 4 * n_blocks);
-    uint32_t* part_at = (uint32_t*)(img + im.off_part_at);
-    qvx_item* items = (qvx_item*)(img + im.off_items);
-    if (im.n_items == 0) {
-        for (size_t t = 0; t < s; t++) part_at[t] = 0xffffffffu;
-        return;
-    }
+    if (im.n_items == 0) return;
     const uint32_t chunk = im.chunk_blocks * L.B;
     const uint32_t group = (uint32_t)(heads / L.kvh), gpk = (group + 7) / 8, groups = L.kvh * gpk;
-    size_t n = 0;
-    uint32_t part = 0;
+    // Longest first, so the short tails fill the end of the launch.  The order is a function
+    // of the lengths alone: a counting sort by tokens, ties in (sequence, group, chunk) order.
+    struct Key { uint32_t tokens, seq, grp, c; };
+    std::vector<Key> keys;
+    keys.reserve(im.n_items);
+    std::vector<uint32_t> part_base(s), counter_base(s);
+    uint32_t part = 0, counter = 0;
     for (size_t t = 0; t < s; t++) {
         uint32_t len = pos[t] + 1u, nch = (len + chunk - 1) / chunk;
-        part_at[t] = nch > 1 ? part : 0xffffffffu;
-        for (uint32_t grp = 0; grp < groups; grp++) {
-            uint32_t kvh = grp / gpk, sub = grp % gpk;
-            for (uint32_t c = 0; c < nch; c++) {
-                qvx_item& it = items[n++];
-                it.seq = (uint32_t)t;
-                it.first = table_at[t] + c * im.chunk_blocks;
-                it.tokens = std::min(chunk, len - c * chunk);
-                it.count = (it.tokens + L.B - 1) / L.B;
-                it.head0 = kvh * group + sub * 8;
-                it.nheads = std::min(8u, group - sub * 8);
-                it.kv_head = kvh;
-                it.part = nch > 1 ? part + grp * nch + c : 0xffffffffu;
-            }
-        }
-        if (nch > 1) part += nch * groups;
+        part_base[t] = part; counter_base[t] = counter;
+        if (nch > 1) { part += nch * groups; counter += groups; }
+        for (uint32_t grp = 0; grp < groups; grp++)
+            for (uint32_t c = 0; c < nch; c++) keys.push_back(Key{std::min(chunk, len - c * chunk), (uint32_t)t, grp, c});
     }
-    // Longest first, so the short tails fill the end of the launch.  Stable: the order is a
-    // function of the lengths alone.
-    std::stable_sort(items, items + n, [](const qvx_item& a, const qvx_item& b) { return a.tokens > b.tokens; });
+    std::stable_sort(keys.begin(), keys.end(), [](const Key& a, const Key& b) { return a.tokens > b.tokens; });
+    uint32_t* items = (uint32_t*)(img + im.off_items);
+    for (size_t n = 0; n < keys.size(); n++) {
+        const Key& k = keys[n];
+        uint32_t t = k.seq, len = pos[t] + 1u, nch = (len + chunk - 1) / chunk;
+        uint32_t kvh = k.grp / gpk, sub = k.grp % gpk;
+        uint32_t* w = items + n * im.item_words;
+        qvx_item_header h;
+        h.seq = t;
+        h.tokens = k.tokens;
+        h.head0 = kvh * group + sub * 8;
+        h.nheads_kv = std::min(8u, group - sub * 8) | (kvh << 16);
+        h.part0 = nch > 1 ? part_base[t] + k.grp * nch : 0xffffffffu;
+        h.part = nch > 1 ? h.part0 + k.c : 0xffffffffu;
+        h.nch = nch;
+        h.counter = nch > 1 ? counter_base[t] + k.grp : 0;
+        memcpy(w, &h, sizeof h);
+        uint32_t count = (k.tokens + L.B - 1) / L.B;
+        const uint32_t* src = blocks + table_at[t] + (size_t)k.c * im.chunk_blocks;
+        for (uint32_t b = 0; b < im.item_words - QVX_ITEM_HEADER_WORDS; b++) w[QVX_ITEM_HEADER_WORDS + b] = b < count ? src[b] : 0;
+    }
 }
 
 static void bind_image(qvx_tables* t, const TableImage& im, void* dmem) {
@@ -285,22 +305,33 @@ static void bind_image(qvx_tables* t, const TableImage& im, void* dmem) {
     t->d_pos = (uint32_t*)(d + im.off_pos);
     t->d_table_at = (uint32_t*)(d + im.off_table_at);
     t->d_blocks = (uint32_t*)(d + im.off_blocks);
-    t->d_part_at = (uint32_t*)(d + im.off_part_at);
-    t->d_items = (qvx_item*)(d + im.off_items);
-    t->n_items = im.n_items; t->n_parts = im.n_parts; t->max_pos = im.max_pos; t->chunk_blocks = im.chunk_blocks;
+    t->d_items = (uint32_t*)(d + im.off_items);
+    t->n_items = im.n_items; t->n_parts = im.n_parts; t->n_counters = im.n_counters;
+    t->max_pos = im.max_pos; t->chunk_blocks = im.chunk_blocks; t->item_words = im.item_words;
 }
 
-static int32_t ensure_partials(qvx_device* dev, size_t floats) {
-    if (floats * 4 <= dev->partials_cap) return QVX_OK;
-    // Work queued earlier may still read the old scratch.
+static int32_t ensure_partials(qvx_device* dev, size_t floats, size_t counters) {
+    if (floats * 4 <= dev->partials_cap && counters <= dev->counters_cap) return QVX_OK;
+    // Work queued earlier may still use the old scratch.
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return check_cuda(dev, e, "partials");
-    if (dev->partials) cudaFree(dev->partials);
-    dev->partials = nullptr; dev->partials_cap = 0;
-    size_t cap = std::max<size_t>(floats * 4 * 5 / 4, 1u << 20);
-    e = cudaMalloc(&dev->partials, cap);
-    if (e != cudaSuccess) return check_cuda(dev, e, "partials");
-    dev->partials_cap = cap;
+    if (floats * 4 > dev->partials_cap) {
+        if (dev->partials) cudaFree(dev->partials);
+        dev->partials = nullptr; dev->partials_cap = 0;
+        size_t cap = std::max<size_t>(floats * 4 * 5 / 4, 1u << 20);
+        e = cudaMalloc(&dev->partials, cap);
+        if (e != cudaSuccess) return check_cuda(dev, e, "partials");
+        dev->partials_cap = cap;
+    }
+    if (counters > dev->counters_cap) {
+        if (dev->counters) cudaFree(dev->counters);
+        dev->counters = nullptr; dev->counters_cap = 0;
+        size_t cap = std::max<size_t>(counters * 2, 4096);
+        e = cudaMalloc((void**)&dev->counters, cap * 4);
+        if (e == cudaSuccess) e = cudaMemset(dev->counters, 0, cap * 4);  // every launch leaves them at zero again
+        if (e != cudaSuccess) return check_cuda(dev, e, "arrival counters");
+        dev->counters_cap = cap;
+    }
     return QVX_OK;
 }
 
@@ -310,9 +341,9 @@ static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, c
     if (variant == QVX_ATTN_SPLIT && !attn_split_supported(t->L, t->heads))
         return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no split attention kernel for this geometry");
     if (variant == QVX_ATTN_EXACT || !split_ok) return launch_attn_exact(dev, t, pool, q, out, s);
-    int32_t rc = ensure_partials(dev, attn_partial_floats(t));
+    int32_t rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
     if (rc) return rc;
-    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, s);
+    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, dev->counters, s);
 }
 
 }  // namespace qvx
@@ -389,6 +420,7 @@ void qvx_close(qvx_device* dev) {
     }
     for (cudaEvent_t ev : dev->event_pool) cudaEventDestroy(ev);
     if (dev->partials) cudaFree(dev->partials);
+    if (dev->counters) cudaFree(dev->counters);
     if (dev->staging) cudaFreeHost(dev->staging);
     if (dev->dstaging) cudaFree(dev->dstaging);
     DeviceExtras* x = nullptr;
@@ -567,6 +599,7 @@ int32_t qvx_tables_create(qvx_device* dev, const qvx_geometry* geo, size_t pool_
     int32_t rc = validate_tables(dev, L, pool_blocks, heads, s, pos, blocks, n_blocks, table_at);
     if (rc) return rc;
     TableImage im = plan_image(L, heads, s, pos, n_blocks, attn_split_supported(L, heads));
+    if (im.max_nch > MAX_CHUNKS) return too_many_chunks(dev, im.max_nch);
     std::vector<uint8_t> img(im.bytes);
     fill_image(im, img.data(), L, heads, s, pos, blocks, n_blocks, table_at);
     void* d = nullptr;
@@ -579,7 +612,7 @@ int32_t qvx_tables_create(qvx_device* dev, const qvx_geometry* geo, size_t pool_
     bind_image(t, im, d);
     t->owns_dmem = true;
     // Grow the scratch now, so a later launch never has to.
-    rc = ensure_partials(dev, attn_partial_floats(t));
+    rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
     if (rc) { cudaFree(d); delete t; return rc; }
     *out = t;
     return QVX_OK;
@@ -641,6 +674,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     const size_t kv_out = (size_t)L.kvh * L.d, q_out = heads * L.d;
     const bool split = attn_split_supported(L, heads) && variant != QVX_ATTN_EXACT;
     TableImage im = plan_image(L, heads, s, pos, n_blocks, split);
+    if (im.max_nch > MAX_CHUNKS) return too_many_chunks(dev, im.max_nch);
     // Staged on the device for this op: the tables image, sync_to, q, k_new, v_new, sync rows, out.
     auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
     const size_t o_img = 0, o_syncto = o_img + im.bytes, o_q = o_syncto + up(4 * n_sync),
@@ -674,7 +708,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     t->owns_dmem = false;
     dev->inflight_tables.push_back(t);
     if (split) {
-        rc = ensure_partials(dev, attn_partial_floats(t));
+        rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
         if (rc) return rc;
     }
 

@@ -143,9 +143,12 @@ struct qvx_device {
     qvx_kernel_times ktimes{};
     std::vector<qvx::TimedLaunch> pending;  // events not read back yet
     std::vector<cudaEvent_t> event_pool;
-    // Scratch the split kernel writes its partial results to, grown on demand.
+    // Scratch the split kernel writes its partial results to, and the arrival counters of the
+    // split sequences (zero between launches), both grown on demand.
     void* partials = nullptr;
     size_t partials_cap = 0;
+    uint32_t* counters = nullptr;
+    size_t counters_cap = 0;
     // Pinned staging for the _host calls, grown on demand; `staging_used` is reset by qvx_wait.
     char* staging = nullptr;
     size_t staging_cap = 0, staging_used = 0;
@@ -178,36 +181,39 @@ int32_t launch_block_copy(qvx_device* dev, const Layout& L, void* pool, const ui
 
 }  // namespace qvx
 
-// One work item of the split kernel: `count` blocks of one sequence's table starting at
-// table entry `first`, for one (kv head, group of <= 8 query heads).
-struct qvx_item {
+// One work item of the split kernel: up to `chunk` blocks of one sequence's table for one
+// (kv head, group of <= 8 query heads).  In device memory an item is ITEM_HEADER_WORDS
+// 32-bit words followed by the ids of its blocks, so that one round trip brings a CTA
+// everything it needs to start its copies.
+#define QVX_ITEM_HEADER_WORDS 8
+struct qvx_item_header {
     uint32_t seq;
-    uint32_t first;      // index into blocks[] of the item's first block
-    uint32_t count;      // blocks in this item
-    uint32_t head0;      // first query head of the group
-    uint32_t nheads;     // query heads in the group (<= 8)
-    uint32_t kv_head;
-    uint32_t tokens;     // valid positions in this item (the last block may be partly filled)
-    uint32_t part;       // index of this item's partial result; 0xffffffff: write `out` directly
+    uint32_t tokens;      // valid positions in this item (the last block may be partly filled)
+    uint32_t head0;       // first query head of the group
+    uint32_t nheads_kv;   // query heads in the group (<= 8) | kv head << 16
+    uint32_t part;        // index of this item's partial result; 0xffffffff: write `out` directly
+    uint32_t part0;       // the partial of the first chunk of this (sequence, group)
+    uint32_t nch;         // chunks of this (sequence, group)
+    uint32_t counter;     // which arrival counter the chunks of this (sequence, group) share
 };
 
 struct qvx_tables {
     qvx_device* dev;
     qvx::Layout L;
-    size_t pool_blocks, heads, s, n_blocks, n_items, n_parts;
+    size_t pool_blocks, heads, s, n_blocks, n_items, n_parts, n_counters;
     uint32_t max_pos;
     uint32_t chunk_blocks;
-    // One device allocation: pos | table_at | blocks | items | part_at
+    uint32_t item_words;  // header + block ids, padded to a multiple of 4 words
+    // One device allocation: pos | table_at | blocks | items
     void* dmem = nullptr;
     size_t dmem_bytes = 0;
     bool owns_dmem = true;
-    uint32_t *d_pos, *d_table_at, *d_blocks, *d_part_at;
-    qvx_item* d_items;
+    uint32_t *d_pos, *d_table_at, *d_blocks, *d_items;
 };
 
 namespace qvx {
 int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                          float* partials, cudaStream_t s);
+                          float* partials, uint32_t* counters, cudaStream_t s);
 int32_t launch_attn_exact(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                           cudaStream_t s);
 size_t attn_partial_floats(const qvx_tables* t);  // floats of scratch the split kernel needs

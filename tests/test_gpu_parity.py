@@ -181,8 +181,10 @@ def test_bad_inputs_are_refused_before_anything_is_written(dev):
         dev.write(fixed, 0, zeros[:16])                                      # only an arena can be written
     with pytest.raises(qd.DeviceError):
         dev.write(buf, len(zeros) - 8, zeros[:16])                           # outside the buffer
-    with pytest.raises(qd.Unsupported):
-        dev.paged_attention(**args(geo=qd.geometry(16, 2, 16, qd.F32, qd.LAYOUT_NATIVE)))
+    with pytest.raises(qd.Unsupported):                                      # native rows are 128-byte multiples
+        dev.paged_attention(**args(geo=qd.geometry(16, 2, 16, qd.F32, qd.LAYOUT_NATIVE), q=c.q[:, :, :16].copy(),
+                                   k_new=c.k_new[:, :32].copy(), v_new=c.v_new[:, :32].copy(),
+                                   sync=c.sync[:, :64].copy()))
     assert np.array_equal(dev.read(buf, 0, len(zeros)), zeros)
     fixed.free()
     buf.free()
@@ -238,7 +240,7 @@ def test_kernel_times_are_counted(dev):
     c = Case(32, 4, 128, 16, "bf16", [600, 100], seed=81)
     c.run_device(dev, variant=qd.ATTN_SPLIT)
     kt = dev.kernel_times()
-    assert kt["sync"][0] == 1 and kt["append"][0] == 1 and kt["attn"][0] == 1 and kt["reduce"][0] == 1
+    assert kt["sync"][0] == 1 and kt["append"][0] == 1 and kt["attn"][0] == 1
     assert kt["attn"][1] > 0
     t = dev.transfers()
-    assert t.submissions >= 1 and t.activations_out >= c.q.nbytes and t.timed >= 4
+    assert t.submissions >= 1 and t.activations_out >= c.q.nbytes and t.timed >= 3
