@@ -1,0 +1,351 @@
+"""Benchmark of the paged KV decode path on the MoE-decoder configuration.
+
+Workload (one "step"): one decode token for each of 64 sequences through 48 layers — per
+layer, append the step's K/V rows to the block pool (KV append) and run paged decode attention
+over the whole context (bf16 KV, 32 query / 4 KV heads of 128, 16-position blocks scattered
+over the pool by a seeded permutation, contexts uniform in [1024, 4096]).  Synthetic data.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+With N > 1 (under torchrun) every rank runs the same workload on its own sequences (the path
+partitions by sequence: no collective in it), `value` is all ranks' tokens over the slowest
+rank's time, scaling "weak".
+
+One JSON line on stdout:
+  value      tokens/s with every input already in device memory (append + attention kernels)
+  e2e        tokens/s through the host-memory call of the C ABI (pinned host buffers in, outputs
+             back to the host), copies inside the timed region
+  roofline   the attention kernel's algorithmic bytes per launch over its mean duration (CUDA
+             events around every launch, inside the timed region), against the measured copy
+             bandwidth of MEASURED_PEAKS.json
+  cpu_baseline  the CPU restatement of the reference's own path, timed on this host (rank 0, N = 1)
+
+--impl reference times only that CPU path, on all host threads, as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from qubivex_b200 import workload as wl  # noqa: E402
+
+METRIC = "paged_kv_decode_tokens_per_s"
+UNIT = "tokens/s"
+SEED = 20261125
+# dram__bytes_read.sum + dram__bytes_write.sum of one attention launch over its algorithmic
+# bytes, from the ncu capture summarised in profiles/ (one layer of this workload).
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.034
+
+
+def env_int(name: str, default: int) -> int:
+    return int(os.environ.get(name, default))
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+def cpu_sample(shape: wl.Shape, lengths: np.ndarray, threads: int, target_s: float, seed: int):
+    """Times the CPU restatement of the reference's path (one task per (token, head) reading the
+    paged pool, as its host path does) on a sample: `n` sequences x 1 layer x 1 decode step,
+    repeated until about `target_s` of wall time.  Returns (seconds per sequence-layer, text)."""
+    import oracle
+
+    n = min(len(lengths), 16)
+    lens = np.asarray(lengths[:n], dtype=np.int64) + 1
+    geo = oracle.geometry(shape.block_tokens, shape.kv_heads, shape.head_dim, oracle.BF16, oracle.LAYOUT_NATIVE)
+    bb = oracle.block_bytes(geo)
+    nb = int(((lens + shape.block_tokens - 1) // shape.block_tokens).sum())
+    rng = np.random.default_rng([seed, 0x77])
+    perm = rng.permutation(nb + 8).astype(np.uint32)
+    tabs = wl.tables_for(lens, shape.block_tokens, perm)
+    scale = wl.value_scale(shape)
+    pool = oracle.narrow(wl.normal(rng, ((nb + 8) * bb // 2,), scale), oracle.BF16).view(np.uint8)
+    q = wl.normal(rng, (n, shape.heads, shape.head_dim), scale)
+    oracle.attn_decode(pool, geo, shape.heads, q[:1], tabs.pos[:1], tabs.blocks, tabs.table_at[:1], threads=threads)  # warm
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        rc, _ = oracle.attn_decode(pool, geo, shape.heads, q, tabs.pos, tabs.blocks, tabs.table_at, threads=threads)
+        assert rc == 0
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= target_s or reps >= 64:
+            break
+    per_seq_layer = dt / (reps * n)
+    text = (f"{n} sequences (contexts {int(lens.min())}-{int(lens.max())}) x 1 layer x 1 decode step, repeated {reps}x "
+            f"({dt:.1f} s); tokens/s = 1 / ({shape.layers} layers x seconds per sequence-layer)")
+    return per_seq_layer, text
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    """The reference arm: the reference's CPU path (its C restatement: the Rust original cannot
+    be built here) on all host threads, same metric and config, a bounded sample per step."""
+    if rank != 0:
+        return
+    shape = wl.C2
+    lengths = wl.contexts(shape, SEED)
+    threads = os.cpu_count() or 1
+    per = []
+    for i in range(args.warmup + args.steps):
+        sec, text = cpu_sample(shape, lengths + i, threads, target_s=max(2.0, 20.0 / max(args.steps, 1)), seed=SEED + i)
+        if i >= args.warmup:
+            per.append(sec)
+    sec = float(np.mean(per))
+    value = 1.0 / (shape.layers * sec)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": shape.batch / value * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": shape.name, "layers": shape.layers, "batch": shape.batch, "heads": shape.heads,
+                   "kv_heads": shape.kv_heads, "head_dim": shape.head_dim, "block_tokens": shape.block_tokens,
+                   "context": [shape.ctx_lo, shape.ctx_hi]},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": text},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+def run_ours(args, rank: int, local_rank: int, world: int) -> None:
+    import torch
+
+    from qubivex_b200 import device as qd
+    from qubivex_b200.device import ptr
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = qd.CudaDevice(local_rank, timing=True)
+    lib = dev.lib
+    shape = wl.C2
+    layers = args.layers or shape.layers
+    s, d, heads, kvh, B = shape.batch, shape.head_dim, shape.heads, shape.kv_heads, shape.block_tokens
+    kv_out = kvh * d
+    geo = qd.geometry(B, kvh, d, qd.BF16, qd.LAYOUT_NATIVE)
+    bb = qd.block_bytes(geo)
+    scale = wl.value_scale(shape)
+    W, K = args.warmup, args.steps
+    We, Ke = min(W, 2), K
+    total_steps = W + K + We + Ke
+    lengths = wl.contexts(shape, SEED + rank)            # positions prefilled per sequence
+    nb_seq = (lengths + total_steps + B - 1) // B          # table entries per sequence, with room to grow
+    blocks_per_layer = int(nb_seq.sum())
+    pool_blocks = blocks_per_layer * layers
+    perm = wl.permutation(pool_blocks, SEED + rank)
+    pool = dev.alloc(pool_blocks * bb)
+    table_at = np.zeros(s, dtype=np.uint32)
+    table_at[1:] = np.cumsum(nb_seq)[:-1]
+    layer_blocks = [perm[l * blocks_per_layer:(l + 1) * blocks_per_layer].copy() for l in range(layers)]
+    stream = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(SEED + rank)
+
+    # ---- prefill through the sync path: every context row of every layer --------------------------
+    seq_of = np.repeat(np.arange(s), lengths)
+    pos_of = np.concatenate([np.arange(n) for n in lengths])
+    n_rows = len(seq_of)
+    chunk = 1 << 16
+    for l in range(layers):
+        blk = layer_blocks[l][table_at[seq_of] + pos_of // B].astype(np.int64)
+        sync_to = torch.from_numpy((blk * B + pos_of % B).astype(np.uint32).view(np.int32)).cuda()
+        for lo in range(0, n_rows, chunk):
+            hi = min(n_rows, lo + chunk)
+            rows = torch.randn((hi - lo, 2 * kv_out), device="cuda", dtype=torch.float32, generator=gen) * scale
+            dev.check(lib.qvx_kv_sync(dev.h, C.byref(geo), C.c_void_p(pool.ptr), pool_blocks, ptr(rows), C.c_void_p(sync_to[lo:hi].data_ptr()),
+                                      hi - lo, C.c_void_p(stream)))
+        torch.cuda.synchronize()
+    del sync_to, rows
+
+    def tables_for_step(t: int, l: int):
+        pos = (lengths + t).astype(np.uint32)
+        out = C.c_void_p()
+        dev.check(lib.qvx_tables_create(dev.h, C.byref(geo), pool_blocks, heads, s, ptr(pos), ptr(layer_blocks[l]), blocks_per_layer,
+                                        ptr(table_at), C.byref(out)))
+        return out
+
+    # ---- value: everything resident ---------------------------------------------------------------
+    tabs = [[tables_for_step(t, l) for l in range(layers)] for t in range(W + K)]
+    q = [torch.randn((s, heads, d), device="cuda", generator=gen) * scale for _ in range(W + K)]
+    kn = [torch.randn((s, kv_out), device="cuda", generator=gen) * scale for _ in range(W + K)]
+    vn = [torch.randn((s, kv_out), device="cuda", generator=gen) * scale for _ in range(W + K)]
+    out = torch.empty((s, heads, d), device="cuda")
+    pool_p, sp = C.c_void_p(pool.ptr), C.c_void_p(stream)
+
+    def step(t: int):
+        for l in range(layers):
+            tb = tabs[t][l]
+            dev.check(lib.qvx_kv_append(dev.h, C.byref(geo), pool_p, pool_blocks, ptr(kn[t]), ptr(vn[t]), lib.qvx_tables_pos(tb),
+                                        lib.qvx_tables_blocks(tb), lib.qvx_tables_table_at(tb), s, sp))
+            dev.check(lib.qvx_attn_decode(dev.h, tb, pool_p, ptr(q[t]), ptr(out), qd.ATTN_AUTO, sp))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for t in range(W):
+        step(t)
+    barrier()
+    dev.reset_kernel_times()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for t in range(W, W + K):
+        step(t)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    kt = dev.kernel_times()
+    value = world * s * K / (ms_total / 1e3)
+    attn_launches, attn_ns = kt["attn"]
+    algo = float(np.mean([wl.algorithmic_bytes(shape, lengths + t + 1) for t in range(W, W + K)]))
+    achieved = algo / (attn_ns / max(attn_launches, 1) * 1e-9) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    launches = sum(v[0] for v in kt.values())
+    for row in tabs:
+        for tb in row:
+            lib.qvx_tables_free(tb)
+
+    # ---- e2e: the host-memory call, pinned buffers, copies timed --------------------------------
+    qh = torch.empty((s, heads, d), pin_memory=True).normal_(0, scale)
+    kh = torch.empty((s, kv_out), pin_memory=True).normal_(0, scale)
+    vh = torch.empty((s, kv_out), pin_memory=True).normal_(0, scale)
+    oh = [torch.empty((s, heads, d), pin_memory=True) for _ in range(layers)]
+    h2d = d2h = 0
+
+    def step_host(t: int):
+        nonlocal h2d, d2h
+        pos = (lengths + t).astype(np.uint32)
+        for l in range(layers):
+            dev.check(lib.qvx_paged_attention_host_async(dev.h, pool.handle, C.byref(geo), heads, s, ptr(qh), ptr(kh), ptr(vh), ptr(pos),
+                                                         ptr(layer_blocks[l]), blocks_per_layer, ptr(table_at), None, None, 0, ptr(oh[l]),
+                                                         qd.ATTN_AUTO))
+        dev.wait()
+        h2d = layers * (qh.numel() * 4 + kh.numel() * 8 + pos.nbytes + table_at.nbytes + layer_blocks[0].nbytes)
+        d2h = layers * oh[0].numel() * 4
+
+    for t in range(W + K, W + K + We):
+        step_host(t)
+    barrier()
+    t0 = time.perf_counter()
+    for t in range(W + K + We, W + K + We + Ke):
+        step_host(t)
+    torch.cuda.synchronize()
+    el = torch.tensor([time.perf_counter() - t0], device="cuda")
+    if dist is not None:
+        dist.all_reduce(el, op=dist.ReduceOp.MAX)
+    e2e_value = world * s * Ke / float(el.item())
+    checksum = float(sum(float(o[0, 0, 0]) for o in oh))
+    assert np.isfinite(checksum)
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": shape.name, "layers": layers, "batch_per_gpu": s, "heads": heads, "kv_heads": kvh, "head_dim": d,
+                   "block_tokens": B, "context": [shape.ctx_lo, shape.ctx_hi], "partition": "by sequence, no collective",
+                   "l2": f"each launch reads {algo / 2**20:.0f} MiB of KV, more than the 126 MB L2; no flush needed",
+                   "pool_gib": pool_blocks * bb / 2**30},
+        "roofline": {"bound": "hbm", "kernel": "attn_stream_kernel (paged decode attention)", "achieved": achieved, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
+                     "traffic": algo * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE, "algorithmic_bytes_per_launch": algo,
+                     "launch_us": attn_ns / max(attn_launches, 1) / 1e3,
+                     "kernels_us_per_launch": {k: (v[1] / v[0] / 1e3 if v[0] else 0.0) for k, v in kt.items() if v[0]}},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "call": "qvx_paged_attention_host_async x layers + qvx_wait per step"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sec, text = cpu_sample(shape, lengths + W + K, os.cpu_count() or 1, target_s=12.0, seed=SEED)
+        line["cpu_baseline"] = {"value": 1.0 / (layers * sec), "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": text}
+    else:
+        line["cpu_baseline"] = None
+    pool.free()
+    dev.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 48 (debugging only)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        if world != args.gpus and world > 1:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+        run_ours(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

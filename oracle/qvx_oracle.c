@@ -269,6 +269,35 @@ static inline float load_elem(const uint8_t *pool, size_t off, uint32_t dtype) {
     return dtype == QVO_BF16 ? qvo_bf16_to_f32(h) : qvo_f16_to_f32(h);
 }
 
+/* One position's key (kv=0) or value (kv=1) row of KV head g, widened to f32: the same
+ * elements as d calls of load_elem(qvo_elem_offset(..)), with the address arithmetic of a row
+ * done once (the reference's kv_key_word / kv_value_word are inlined const fns). */
+static void load_row(const uint8_t *pool, const qvo_geometry *geo, size_t at, int kv, size_t g, float *out) {
+    size_t B = geo->block_tokens, d = geo->head_dim, kvh = geo->kv_heads, e = elem_size(geo->dtype);
+    size_t b = at / B, slot = at % B, kv_out = kvh * d;
+    const uint8_t *p;
+    size_t stride;
+    size_t swz = 0;
+    if (geo->layout == QVO_LAYOUT_REFERENCE) {
+        size_t w = b * (2 * B * kv_out);
+        if (kv) { w += B * kv_out + slot * kv_out + g * d; stride = e; }
+        else { w += (g * d) * B + slot; stride = B * e; }
+        p = pool + w * e;
+    } else {
+        size_t row = d * e, page = B * row;
+        p = pool + b * (kvh * 2 * page) + g * (2 * page) + (size_t)kv * page + slot * row;
+        stride = e;
+        swz = (slot & 7) << 4;
+    }
+    if (geo->dtype == QVO_F32) {
+        for (size_t i = 0; i < d; i++) memcpy(out + i, p + ((i * stride) ^ swz), 4);
+    } else if (geo->dtype == QVO_BF16) {
+        for (size_t i = 0; i < d; i++) { uint16_t h; memcpy(&h, p + ((i * stride) ^ swz), 2); out[i] = qvo_bf16_to_f32(h); }
+    } else {
+        for (size_t i = 0; i < d; i++) { uint16_t h; memcpy(&h, p + ((i * stride) ^ swz), 2); out[i] = qvo_f16_to_f32(h); }
+    }
+}
+
 /* The `put` closure, crates/qubivex-backend-cpu/src/sim.rs:377-384: one position's key
  * row and value row (kv_out f32 each) into the pool, narrowed to the pool's dtype. */
 static void put(uint8_t *pool, const qvo_geometry *geo, size_t at, const float *k, const float *v) {
@@ -331,11 +360,10 @@ static void attend_tokens(const uint8_t *pool, const qvo_geometry *geo, size_t h
         float *scores = malloc(sizeof(float) * n);
         for (size_t p = 0; p < n; p++) {
             size_t to = at_of(geo, blocks, table_at, t, p);
-            for (size_t g = 0; g < kvh; g++)
-                for (size_t i = 0; i < d; i++) {
-                    ks[(g * n + p) * d + i] = load_elem(pool, qvo_elem_offset(geo, to, 0, g, i), geo->dtype);
-                    vs[(g * n + p) * d + i] = load_elem(pool, qvo_elem_offset(geo, to, 1, g, i), geo->dtype);
-                }
+            for (size_t g = 0; g < kvh; g++) {
+                load_row(pool, geo, to, 0, g, ks + (g * n + p) * d);
+                load_row(pool, geo, to, 1, g, vs + (g * n + p) * d);
+            }
         }
         for (size_t hd = 0; hd < heads; hd++) {
             size_t g = hd / group;
@@ -399,10 +427,8 @@ static void *par_worker(void *arg) {
         }
         for (size_t p = 0; p < n; p++) {
             size_t to = at_of(j->geo, j->blocks, j->table_at, t, p);
-            for (size_t i = 0; i < d; i++) {
-                k[p * d + i] = load_elem(j->pool, qvo_elem_offset(j->geo, to, 0, g, i), j->geo->dtype);
-                v[p * d + i] = load_elem(j->pool, qvo_elem_offset(j->geo, to, 1, g, i), j->geo->dtype);
-            }
+            load_row(j->pool, j->geo, to, 0, g, k + p * d);
+            load_row(j->pool, j->geo, to, 1, g, v + p * d);
         }
         qvo_attend(j->q + t * q_out + hd * d, k, v, d, n - 1, j->att + t * q_out + hd * d, scores);
     }

@@ -17,8 +17,11 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = PKG / "csrc"
-LIB = PKG / "lib" / "libqvx_cuda.so"
-OBJ = ROOT / "build" / "obj"
+# QVX_LIB / QVX_NVCC_EXTRA build and load a variant library (kernel experiments); unset, the
+# shipped library is qubivex_b200/lib/libqvx_cuda.so.
+LIB = Path(os.environ["QVX_LIB"]).resolve() if os.environ.get("QVX_LIB") else PKG / "lib" / "libqvx_cuda.so"
+OBJ = ROOT / "build" / ("obj-" + LIB.stem if os.environ.get("QVX_LIB") else "obj")
+EXTRA = os.environ.get("QVX_NVCC_EXTRA", "").split()
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
@@ -27,6 +30,7 @@ SOURCES = {
     "kv_rows.cu": [],
     "block_copy.cu": [],
     "attn_split.cu": [],
+    "attn_stream.cu": [],
     "attn_exact.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],
     "runtime.cpp": [],
 }
@@ -55,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         src = CSRC / name
         obj = OBJ / (name.rsplit(".", 1)[0] + ".o")
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc(), *ARCH, *COMMON, *extra]
+            cmd = [nvcc(), *ARCH, *COMMON, *extra, *EXTRA]
             if verbose:
                 cmd += ["-Xptxas", "-v"]
             cmd += ["-c", str(src), "-o", str(obj)]

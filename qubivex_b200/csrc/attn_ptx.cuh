@@ -1,0 +1,143 @@
+// PTX wrappers and argument structs shared by the decode-attention kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "qvx_common.cuh"
+
+namespace qvx {
+
+constexpr int TILE = 16;              // positions per tile
+constexpr uint32_t NO_PART = 0xffffffffu;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+// Status word values a kernel can leave (0 = fine).
+constexpr int STATUS_WAIT_TIMEOUT = 1;
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Global -> this CTA's shared memory, completion counted in bytes on `bar`.  No multicast.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after WAIT_LIMIT polls and reports it instead of spinning for ever.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 1024) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+template <int DT>
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (DT == QVX_BF16) {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    } else {
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+}
+template <int DT>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+    if constexpr (DT == QVX_BF16) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    } else {
+        __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+}
+// x = hi + lo with hi the nearest 16-bit value and lo the rounded remainder: two tensor-core
+// passes then carry ~16 bits of mantissa instead of 8 (bf16) or 11 (f16).
+template <int DT>
+__device__ __forceinline__ void split16(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    if constexpr (DT == QVX_BF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+        float2 hf = __bfloat1622float2(h);
+        __nv_bfloat162 l = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
+        hi = *reinterpret_cast<uint32_t*>(&h);
+        lo = *reinterpret_cast<uint32_t*>(&l);
+    } else {
+        __half2 h = __floats2half2_rn(x0, x1);
+        float2 hf = __half22float2(h);
+        __half2 l = __floats2half2_rn(x0 - hf.x, x1 - hf.y);
+        hi = *reinterpret_cast<uint32_t*>(&h);
+        lo = *reinterpret_cast<uint32_t*>(&l);
+    }
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---- kernel arguments --------------------------------------------------------------------
+struct SplitArgs {
+    const uint8_t* pool;
+    const float* q;             // [token][head][d]
+    float* out;                 // [token][head][d]
+    float* partials;            // n_parts x (8*d + 16): acc[8][d], m[8], l[8]
+    uint32_t* counters;         // one per split (sequence, group): arrivals so far; zero between launches
+    const uint32_t* items;      // n_items x item_words: header, then the item's block ids
+    int* status;                // a kernel that gave up a wait leaves a code here
+    uint64_t block_bytes;
+    uint32_t page_bytes, row_bytes, tiles_per_block, heads, d, item_words;
+    float scale_log2;           // (1 / sqrt(d)) * log2(e)
+};
+
+struct Item {
+    uint32_t seq, tokens, head0, nheads, kv_head, part, part0, nch, counter;
+};
+__device__ __forceinline__ Item load_item(const uint32_t* w) {
+    uint4 a = *reinterpret_cast<const uint4*>(w), b = *reinterpret_cast<const uint4*>(w + 4);
+    Item it;
+    it.seq = a.x; it.tokens = a.y; it.head0 = a.z; it.nheads = a.w & 0xffffu; it.kv_head = a.w >> 16;
+    it.part = b.x; it.part0 = b.y; it.nch = b.z; it.counter = b.w;
+    return it;
+}
+
+
+}  // namespace qvx

@@ -1,0 +1,562 @@
+// Paged decode attention over 16-bit pools: a persistent, warp-specialised streaming kernel.
+//
+// Computes what `attn_decode.comp` (crates/qubivex-backend-vulkan/shaders/attn_decode.comp:60-175)
+// and the gather + `attend` of the CPU device (crates/qubivex-backend-cpu/src/sim.rs:400-429,
+// crates/qubivex-compute/src/math.rs:142-155) compute, with an online softmax and the context
+// split into chunks: results agree within a tolerance, not bit for bit.
+//
+// The kernel is HBM bound (per position per kv head: 2*d*e bytes, 4*d*G flops), so it is
+// organised around keeping bulk copies in flight, not around the arithmetic:
+//
+//   - CTAs are persistent.  Each takes work items (a chunk of one sequence for one kv head
+//     and its group of <= 8 query heads) from a device-wide queue, longest first, until
+//     the queue is empty; a CTA never waits for another CTA.
+//   - One producer warp per CTA walks the queue one item ahead of its own copies: the next
+//     item's index (an atomic) and record (header + block ids, one bulk copy) are in flight
+//     while it issues the current item's tiles.  For every tile of 16 positions it issues bulk
+//     async copies (cp.async.bulk global -> shared, completion counted on an mbarrier) of the
+//     key rows and the value rows, contiguous in the native pool layout, into a ring of
+//     stages shared by the CTA.  It runs ahead across item boundaries, so neither the
+//     start-up nor the wind-down of an item drains the memory pipe.
+//   - The consumer warps take the tiles in turn (tile n of the stream -> warp n mod CW), each
+//     with its own online-softmax state: S^T = K Q^T for the tile (16 positions x 8 heads,
+//     m16n8k16 with K as the A operand straight from the swizzled page), then
+//     O^T += V^T P^T (V through ldmatrix.trans, P transposed in registers by movmatrix).
+//     Every key and value byte is read from shared memory exactly once.
+//   - At the end of an item the consumers merge their states through shared memory (two
+//     named barriers among themselves; the producer keeps streaming the next item meanwhile)
+//     and write the output, or the chunk's partial result.
+//   - An epilogue warp per CTA takes over from there for a sequence that was split into
+//     several chunks: the device-wide fence, the count of the chunk's arrival (one counter per
+//     (sequence, group); nobody waits on it) and, in whichever CTA the last chunk arrives, the
+//     merge of the partials in chunk order, so the sum order is fixed.  The consumers are on
+//     the next item's tiles meanwhile.
+//
+// bf16 carries 8 mantissa bits: queries and probabilities go through the tensor cores as a
+// 16-bit value plus a 16-bit remainder (two passes), which keeps the result within 1e-5 of the
+// f32 arithmetic instead of 5e-3.  f16's 11 bits need one pass.
+#include "attn_ptx.cuh"
+
+namespace qvx {
+
+#ifndef QVX_CW
+#define QVX_CW 4                               // consumer warps per CTA
+#endif
+constexpr int CW = QVX_CW;
+constexpr int CT = CW * 32;                    // consumer threads
+constexpr int STREAM_THREADS = CT + 64;        // + the producer warp and the epilogue warp
+constexpr int MAIL_SLOTS = 4;
+constexpr int Q_SLOTS = 2;
+constexpr int REC_SLOTS = 4;
+constexpr int REC_WORDS = 144;                 // header + up to 136 block ids
+
+struct StreamArgs {
+    const uint8_t* pool;
+    const float* q;
+    float* out;
+    float* partials;        // per partial: acc[8][d], then CW copies of { m[8], l[8] }
+    uint32_t* counters;     // per split (sequence, group): CW arrival counters, zero between launches
+    uint32_t* queue;        // [0] next item, [1] CTAs done; both zero between launches
+    const uint32_t* items;
+    int* status;
+    uint64_t block_bytes;
+    uint32_t page_bytes, tiles_per_block, heads, item_words, n_items;
+    float scale_log2;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory"); }
+
+template <int D>
+struct StreamSmem {
+    static constexpr int ctas_per_sm = D <= 128 ? 2 : 1;
+    static constexpr uint32_t budget = (227u * 1024u) / ctas_per_sm - 1024u;
+    static constexpr uint32_t tile_bytes = TILE * D * 2;
+    static constexpr uint32_t stage_bytes = 2 * tile_bytes;
+    static constexpr uint32_t q_stride = D * 4 + 16;  // padded rows: fragment reads hit 32 distinct banks
+    static constexpr uint32_t res_floats = 16 + 8 * D;  // one warp's state: m[8], l[8], acc[8][D]
+    static constexpr uint32_t res_bytes = CW * res_floats * 4;
+    static constexpr uint32_t q_bytes = Q_SLOTS * 8 * q_stride;
+    static constexpr uint32_t rec_bytes = REC_SLOTS * REC_WORDS * 4;
+    static constexpr uint32_t fixed = res_bytes + q_bytes + rec_bytes + 1024;
+    static constexpr uint32_t stages_fit = (budget - fixed) / stage_bytes;
+    // A multiple of CW: tile n goes to stage n % stages and to warp n % CW, so a stage is
+    // always read by the same warp and a warp waits for its stages' phases strictly in order
+    // (waiting two phases ahead on an mbarrier parity would return at once).
+    static constexpr uint32_t stages = (stages_fit > 4 * CW ? 4 * CW : stages_fit) / CW * CW;
+    static constexpr uint32_t ring_off = 0;
+    static constexpr uint32_t res_off = stages * stage_bytes;
+    static constexpr uint32_t q_off = res_off + res_bytes;
+    static constexpr uint32_t rec_off = q_off + q_bytes;
+    static constexpr uint32_t bar_off = rec_off + rec_bytes;
+    // full[stages], empty[stages], qfull[Q_SLOTS], qempty[Q_SLOTS], rec[REC_SLOTS],
+    // mail_full[MAIL_SLOTS], mail_free[MAIL_SLOTS], then the abort word and the mailbox
+    static constexpr uint32_t n_bars = 2 * stages + 2 * Q_SLOTS + REC_SLOTS + 2 * MAIL_SLOTS;
+    static constexpr uint32_t abort_off = bar_off + n_bars * 8;
+    static constexpr uint32_t mail_off = abort_off + 16;
+    static constexpr uint32_t total = mail_off + MAIL_SLOTS * 32;
+    static_assert(stages >= CW, "the ring needs a stage per consumer warp");
+};
+
+// What the consumers tell the epilogue warp about a chunk whose partial they have stored.
+struct Mail {
+    uint32_t seq, head0, nheads, part0, nch, counter, stop, pad;
+};
+
+// Run by the epilogue warp: counts the arrival of one chunk's partial and, if it was the last
+// of its (sequence, group) to arrive, merges the partials over the chunks in chunk order.
+template <int D>
+__device__ __forceinline__ void deliver(const StreamArgs& a, const Mail& it, uint32_t lane) {
+    constexpr uint32_t F4 = 8 * D / 4;
+    constexpr uint32_t PART_STRIDE = 8 * D + 16;
+    __threadfence();  // the consumers' stores (seen through the mailbox barrier) are visible device-wide first
+    __syncwarp();
+    uint32_t last = 0;
+    if (lane == 0) last = atomicAdd(a.counters + it.counter, 1u) == it.nch - 1 ? 1u : 0u;
+    if (!__shfl_sync(0xffffffffu, last, 0)) return;
+    __threadfence();
+    const float* p0 = a.partials + (size_t)it.part0 * PART_STRIDE;
+    const float* ml = p0 + 8 * D;
+    const uint32_t hl = lane & 7;
+    float M = -INFINITY, L = 0.f;
+    for (uint32_t c = lane >> 3; c < it.nch; c += 4) M = fmaxf(M, __ldcg(ml + (size_t)c * PART_STRIDE + hl));
+    M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
+    M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+    for (uint32_t c = lane >> 3; c < it.nch; c += 4)
+        L = fmaf(__ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl), ex2(__ldcg(ml + (size_t)c * PART_STRIDE + hl) - M), L);
+    L += __shfl_xor_sync(0xffffffffu, L, 8);
+    L += __shfl_xor_sync(0xffffffffu, L, 16);
+    // Lane x owns float4 column x of every head when D = 128; in general output i = lane + 32 j.
+    // All of a lane's outputs advance together, two chunks at a time, so that 2 * NJ 16-byte
+    // loads are in flight per lane: the merge is a chain of L2 round trips and nothing else.
+    constexpr int NJ = F4 / 32;
+    float4 acc[NJ];
+    float Mh[NJ], Lh[NJ];
+    uint32_t off[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        const uint32_t i = lane + j * 32, hh = i / (D / 4);
+        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        Mh[j] = __shfl_sync(0xffffffffu, M, hh);
+        Lh[j] = __shfl_sync(0xffffffffu, L, hh);
+        off[j] = hh * D + (i % (D / 4)) * 4;
+    }
+    for (uint32_t c = 0; c < it.nch; c += 2) {
+        const bool two = c + 1 < it.nch;
+        const float* pa = p0 + (size_t)c * PART_STRIDE;
+        const float* pb = two ? pa + PART_STRIDE : pa;
+        float4 va[NJ], vb[NJ];
+        float wa[NJ], wb[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const uint32_t hh = (lane + j * 32) / (D / 4);
+            va[j] = __ldcg(reinterpret_cast<const float4*>(pa + off[j]));
+            vb[j] = __ldcg(reinterpret_cast<const float4*>(pb + off[j]));
+            wa[j] = __ldcg(pa + 8 * D + hh);
+            wb[j] = __ldcg(pb + 8 * D + hh);
+        }
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const float ga = ex2(wa[j] - Mh[j]), gb = two ? ex2(wb[j] - Mh[j]) : 0.f;
+            acc[j].x = fmaf(va[j].x, ga, acc[j].x); acc[j].y = fmaf(va[j].y, ga, acc[j].y);
+            acc[j].z = fmaf(va[j].z, ga, acc[j].z); acc[j].w = fmaf(va[j].w, ga, acc[j].w);
+            acc[j].x = fmaf(vb[j].x, gb, acc[j].x); acc[j].y = fmaf(vb[j].y, gb, acc[j].y);
+            acc[j].z = fmaf(vb[j].z, gb, acc[j].z); acc[j].w = fmaf(vb[j].w, gb, acc[j].w);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        const uint32_t hh = (lane + j * 32) / (D / 4);
+        if (hh < it.nheads)
+            *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0) * D + off[j]) =
+                make_float4(acc[j].x / Lh[j], acc[j].y / Lh[j], acc[j].z / Lh[j], acc[j].w / Lh[j]);
+    }
+    if (lane == 0) a.counters[it.counter] = 0;  // ready for the next launch
+}
+
+template <int DT, int D, bool PRECISE>
+__global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) attn_stream_kernel(StreamArgs a) {
+    using SM = StreamSmem<D>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t full0 = sbase + SM::bar_off, empty0 = full0 + SM::stages * 8;
+    const uint32_t qfull0 = empty0 + SM::stages * 8, qempty0 = qfull0 + Q_SLOTS * 8, recbar0 = qempty0 + Q_SLOTS * 8;
+    const uint32_t mfull0 = recbar0 + REC_SLOTS * 8, mfree0 = mfull0 + MAIL_SLOTS * 8;
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + SM::abort_off);
+    volatile Mail* mailbox = reinterpret_cast<volatile Mail*>(smem + SM::mail_off);
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < SM::stages; s++) { mbar_init(full0 + s * 8, 1); mbar_init(empty0 + s * 8, 1); }
+        for (uint32_t s = 0; s < Q_SLOTS; s++) { mbar_init(qfull0 + s * 8, 1); mbar_init(qempty0 + s * 8, CW); }
+        for (uint32_t s = 0; s < REC_SLOTS; s++) mbar_init(recbar0 + s * 8, 1);
+        for (uint32_t s = 0; s < MAIL_SLOTS; s++) { mbar_init(mfull0 + s * 8, CW); mbar_init(mfree0 + s * 8, 1); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    if (warp == CW) {
+        // ================================ producer ================================
+        // Only lane 0 works; the other lanes leave at once.
+        if (lane != 0) return;
+        uint32_t* rec_base = reinterpret_cast<uint32_t*>(smem + SM::rec_off);
+        const uint32_t rec_bytes_one = a.item_words * 4;
+        // Fetches item `idx` into record slot j % REC_SLOTS (or writes the end-of-queue record).
+        auto fetch = [&](uint32_t j, uint32_t idx) {
+            const uint32_t slot = j % REC_SLOTS;
+            if (idx < a.n_items) {
+                mbar_expect_tx(recbar0 + slot * 8, rec_bytes_one);
+                bulk_g2s(sbase + SM::rec_off + slot * REC_WORDS * 4, a.items + (size_t)idx * a.item_words, rec_bytes_one,
+                         recbar0 + slot * 8);
+            } else {
+                rec_base[slot * REC_WORDS + 1] = 0;  // an item of no positions: the end of the queue
+                mbar_arrive(recbar0 + slot * 8);
+            }
+        };
+        uint32_t n = 0;          // tiles issued so far, over all items
+        bool failed = false;
+        uint32_t idx_next = atomicAdd(a.queue, 1u);
+        fetch(0, idx_next);
+        bool queue_dry = idx_next >= a.n_items;
+        idx_next = queue_dry ? idx_next : atomicAdd(a.queue, 1u);  // item 1: in flight while item 0 is set up
+        for (uint32_t k = 0;; k++) {
+            const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
+            if (!mbar_wait(recbar0 + rslot * 8, (k / REC_SLOTS) & 1)) { failed = true; break; }
+            const uint32_t* rec = rec_base + rslot * REC_WORDS;
+            const uint32_t seq = rec[0], tokens = rec[1], head0 = rec[2], nheads = rec[3] & 0xffffu, kvh = rec[3] >> 16;
+            // The consumers are done with the queries of item k - Q_SLOTS (and so with every
+            // record before it).
+            if (!mbar_wait(qempty0 + qslot * 8, ((k / Q_SLOTS) & 1) ^ 1)) { failed = true; break; }
+            if (tokens == 0) {
+                mbar_arrive(qfull0 + qslot * 8);  // hand the end-of-queue record to the consumers
+                break;
+            }
+            mbar_expect_tx(qfull0 + qslot * 8, nheads * D * 4);
+            const float* qp = a.q + ((size_t)seq * a.heads + head0) * D;
+            for (uint32_t h = 0; h < nheads; h++)
+                bulk_g2s(sbase + SM::q_off + (qslot * 8 + h) * SM::q_stride, qp + (size_t)h * D, D * 4, qfull0 + qslot * 8);
+            // Item k + 1: its index has had a whole item's time to come back.
+            fetch(k + 1, idx_next);
+            if (!queue_dry) {
+                queue_dry = idx_next >= a.n_items;
+                if (!queue_dry) idx_next = atomicAdd(a.queue, 1u);
+            }
+            const uint32_t ntiles = (tokens + TILE - 1) / TILE;
+            const uint8_t* base = a.pool + (uint64_t)kvh * 2u * a.page_bytes;
+            for (uint32_t tau = 0; tau < ntiles; tau++, n++) {
+                const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
+                if (!mbar_wait(empty0 + st * 8, ph ^ 1)) { failed = true; break; }
+                const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + tau / a.tiles_per_block];
+                const uint8_t* src = base + (uint64_t)blk * a.block_bytes + (uint64_t)(tau % a.tiles_per_block) * SM::tile_bytes;
+                const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
+                mbar_expect_tx(full0 + st * 8, SM::stage_bytes);
+                if (a.page_bytes == SM::tile_bytes) {  // one tile per block: its values follow its keys
+                    bulk_g2s(dst, src, SM::stage_bytes, full0 + st * 8);
+                } else {
+                    bulk_g2s(dst, src, SM::tile_bytes, full0 + st * 8);
+                    bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, full0 + st * 8);
+                }
+            }
+            if (failed) break;
+        }
+        if (failed) {
+            *abort_flag = 1;
+            atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+        }
+        // The last CTA to run out of work leaves the queue ready for the next launch.
+        const uint32_t done = atomicAdd(a.queue + 1, 1u);
+        if (done == gridDim.x - 1) { a.queue[0] = 0; a.queue[1] = 0; }
+        return;
+    }
+
+    if (warp == CW + 1) {
+        // ================================ epilogue ================================
+        // Takes the chunks whose partials the consumers have stored, one mail each, and does
+        // what would otherwise stall them: the device-wide fence, the arrival count and, for
+        // the last chunk of a sequence to arrive, the merge.
+        for (uint32_t kp = 0;; kp++) {
+            const uint32_t ms = kp % MAIL_SLOTS;
+            if (!__all_sync(0xffffffffu, mbar_wait(mfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;  // the abort path
+            Mail m;
+            m.seq = mailbox[ms].seq; m.head0 = mailbox[ms].head0; m.nheads = mailbox[ms].nheads; m.part0 = mailbox[ms].part0;
+            m.nch = mailbox[ms].nch; m.counter = mailbox[ms].counter; m.stop = mailbox[ms].stop;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(mfree0 + ms * 8);
+            if (m.stop) return;
+            deliver<D>(a, m, lane);
+        }
+    }
+
+    // ================================ consumers ================================
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t mid = lane >> 3, r8 = lane & 7;
+    const uint32_t k_row = r8 + 8 * (mid & 1), k_chunk = mid >> 1;  // keys: A = K
+    const uint32_t v_row = r8 + 8 * (mid >> 1), v_chunk = mid & 1;  // values: A = V^T (ldmatrix.trans)
+    const uint32_t tid_c = warp * 32 + lane;
+    constexpr uint32_t F4 = 8 * D / 4;                 // float4 values of one item's output
+    constexpr uint32_t PART_STRIDE = 8 * D + 16;  // floats per partial: acc[8][D], m[8], l[8]
+    float* res_all = reinterpret_cast<float*>(smem + SM::res_off);
+    float* res = res_all + warp * SM::res_floats;
+    uint32_t nbase = 0;   // tiles of the items before this one
+    uint32_t kp = 0;      // mails sent to the epilogue warp so far
+    bool dead = false;    // this warp gave up a wait: it only keeps the barriers company from here on
+    for (uint32_t k = 0;; k++) {
+        const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
+        Item it{};
+        if (!dead && !__all_sync(0xffffffffu, mbar_wait(qfull0 + qslot * 8, (k / Q_SLOTS) & 1))) dead = true;
+        // The record came by bulk copy: observe its own barrier too before reading it.
+        if (!dead && !__all_sync(0xffffffffu, mbar_wait(recbar0 + rslot * 8, (k / REC_SLOTS) & 1))) dead = true;
+        if (!dead) {
+            const uint32_t* rec = reinterpret_cast<const uint32_t*>(smem + SM::rec_off) + rslot * REC_WORDS;
+            it.seq = rec[0]; it.tokens = rec[1]; it.head0 = rec[2]; it.nheads = rec[3] & 0xffffu; it.kv_head = rec[3] >> 16;
+            it.part = rec[4]; it.part0 = rec[5]; it.nch = rec[6]; it.counter = rec[7];
+            if (it.tokens == 0) break;  // the end of the queue: every consumer warp reads the same record
+        }
+        float o[D / 16][4];
+#pragma unroll
+        for (int m = 0; m < D / 16; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; }
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // heads 2t and 2t+1
+        if (!dead) {
+            // Q^T fragments (the B operand): this lane holds head g, dims 16*ks + 2t + {0,1,8,9}.
+            uint32_t qf[D / 16][2], ql[D / 16][2];
+            {
+                const bool live = g < it.nheads;
+                const float* qrow = reinterpret_cast<const float*>(smem + SM::q_off + (qslot * 8 + g) * SM::q_stride);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ks++) {
+                    float2 x0 = make_float2(0.f, 0.f), x1 = x0;
+                    if (live) {
+                        x0 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t);
+                        x1 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t + 8);
+                    }
+                    split16<DT>(x0.x, x0.y, qf[ks][0], ql[ks][0]);
+                    split16<DT>(x1.x, x1.y, qf[ks][1], ql[ks][1]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(qempty0 + qslot * 8);  // the producer may reuse this query slot
+
+            const uint32_t ntiles = (it.tokens + TILE - 1) / TILE;
+            // Tiles are dealt to the warps by their number in the whole stream, not in the item.
+            for (uint32_t tau = (warp + CW - nbase % CW) % CW; tau < ntiles; tau += CW) {
+                const uint32_t n = nbase + tau;
+                const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
+                if (!__all_sync(0xffffffffu, mbar_wait(full0 + st * 8, ph))) { dead = true; break; }
+                const uint32_t kt = sbase + SM::ring_off + st * SM::stage_bytes, vt = kt + SM::tile_bytes;
+                const uint32_t valid = min((uint32_t)TILE, it.tokens - tau * TILE);
+#ifndef QVX_EXPERIMENT_NOCOMPUTE
+                // S^T = K Q^T; the value pass and the remainder pass accumulate separately so the
+                // chain of dependent tensor-core ops is half as long.
+                float sc[4] = {0.f, 0.f, 0.f, 0.f}, sr[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ks++) {
+                    uint32_t af[4];
+                    ldmatrix_x4(kt + k_row * (D * 2) + (((2 * ks + k_chunk) ^ (k_row & 7)) << 4), af);
+                    mma_16816<DT>(sc, af, qf[ks][0], qf[ks][1]);
+                    if constexpr (PRECISE) mma_16816<DT>(sr, af, ql[ks][0], ql[ks][1]);
+                }
+                if constexpr (PRECISE) { sc[0] += sr[0]; sc[1] += sr[1]; sc[2] += sr[2]; sc[3] += sr[3]; }
+                if (valid < TILE) {
+                    // The tail of the last block: unwritten slots hold whatever the pool held before.
+                    if (g >= valid) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
+                    if (g + 8 >= valid) { sc[2] = -INFINITY; sc[3] = -INFINITY; }
+                    // 0 * NaN is NaN: clear the value rows no probability reaches.
+                    for (uint32_t c = valid * (D * 2 / 16) + lane; c < TILE * (D * 2 / 16); c += 32)
+                        *reinterpret_cast<uint4*>(smem + SM::ring_off + st * SM::stage_bytes + SM::tile_bytes + c * 16) =
+                            make_uint4(0, 0, 0, 0);
+                    fence_proxy_async();  // these generic writes precede the bulk copy that reuses the stage
+                    __syncwarp();
+                }
+                // Online softmax in base 2; this lane sees heads 2t, 2t+1 at positions g, g+8.
+                float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
+#pragma unroll
+                for (int sh = 4; sh <= 16; sh <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+                }
+                const float mn0 = fmaxf(m0, mx0 * a.scale_log2), mn1 = fmaxf(m1, mx1 * a.scale_log2);
+                const float al0 = ex2(m0 - mn0), al1 = ex2(m1 - mn1);
+                m0 = mn0; m1 = mn1;
+                const float p0 = ex2(fmaf(sc[0], a.scale_log2, -mn0)), p1 = ex2(fmaf(sc[1], a.scale_log2, -mn1));
+                const float p2 = ex2(fmaf(sc[2], a.scale_log2, -mn0)), p3 = ex2(fmaf(sc[3], a.scale_log2, -mn1));
+                l0 = fmaf(l0, al0, p0 + p2);
+                l1 = fmaf(l1, al1, p1 + p3);
+                // P^T as the B operand: (position g; heads 2t,2t+1) -> (head g; positions 2t,2t+1).
+                uint32_t ph0, pl0, ph1, pl1;
+                split16<DT>(p0, p1, ph0, pl0);
+                split16<DT>(p2, p3, ph1, pl1);
+                const uint32_t pb0 = movmatrix_trans(ph0), pb1 = movmatrix_trans(ph1);
+                uint32_t pc0 = 0, pc1 = 0;
+                if constexpr (PRECISE) { pc0 = movmatrix_trans(pl0); pc1 = movmatrix_trans(pl1); }
+                // O^T = O^T * alpha + V^T P^T
+#pragma unroll
+                for (int mt = 0; mt < D / 16; mt++) {
+                    o[mt][0] *= al0; o[mt][1] *= al1; o[mt][2] *= al0; o[mt][3] *= al1;
+                    uint32_t vf[4];
+                    ldmatrix_x4_trans(vt + v_row * (D * 2) + (((2 * mt + v_chunk) ^ (v_row & 7)) << 4), vf);
+                    mma_16816<DT>(o[mt], vf, pb0, pb1);
+                    if constexpr (PRECISE) mma_16816<DT>(o[mt], vf, pc0, pc1);
+                }
+#else
+                (void)kt; (void)vt; (void)valid; (void)k_row; (void)k_chunk; (void)v_row; (void)v_chunk;
+#endif
+                __syncwarp();  // every lane is done with this stage
+                if (lane == 0) mbar_arrive(empty0 + st * 8);
+            }
+            nbase += ntiles;
+        }
+        // Row sums over the positions held by the other lanes of the same t.
+#pragma unroll
+        for (int sh = 4; sh <= 16; sh <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+        }
+        if (dead) {
+            *abort_flag = 1;
+            if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+        }
+        // ---- the consumers' states meet in shared memory --------------------------------------
+        consumer_barrier();  // the previous item's merge has read everything it needed
+        if (*abort_flag) return;  // uniform: every consumer warp sees the flag after the barrier
+        if (g == 0) {
+            res[2 * t] = m0; res[2 * t + 1] = m1;
+            res[8 + 2 * t] = l0; res[8 + 2 * t + 1] = l1;
+        }
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+            res[16 + (2 * t) * D + 16 * mt + g] = o[mt][0];
+            res[16 + (2 * t + 1) * D + 16 * mt + g] = o[mt][1];
+            res[16 + (2 * t) * D + 16 * mt + g + 8] = o[mt][2];
+            res[16 + (2 * t + 1) * D + 16 * mt + g + 8] = o[mt][3];
+        }
+        consumer_barrier();
+        // Each thread merges its share of the item's float4 outputs over the CW warps.
+        const bool direct = it.part == NO_PART;
+        float* pbase = direct ? nullptr : a.partials + (size_t)it.part * PART_STRIDE;
+#pragma unroll
+        for (uint32_t j = 0; j < (F4 + CT - 1) / CT; j++) {
+            const uint32_t i = tid_c + j * CT;
+            if (i >= F4) break;
+            const uint32_t h = i / (D / 4), x = (i % (D / 4)) * 4;
+            if (h >= it.nheads) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < CW; w++) M = fmaxf(M, res_all[w * SM::res_floats + h]);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float l = 0.f;
+#pragma unroll
+            for (int w = 0; w < CW; w++) {
+                const float* r = res_all + w * SM::res_floats;
+                const float wg = ex2(r[h] - M);
+                const float4 v = *reinterpret_cast<const float4*>(r + 16 + h * D + x);
+                acc.x = fmaf(v.x, wg, acc.x); acc.y = fmaf(v.y, wg, acc.y);
+                acc.z = fmaf(v.z, wg, acc.z); acc.w = fmaf(v.w, wg, acc.w);
+                l = fmaf(r[8 + h], wg, l);
+            }
+            if (direct) {
+                *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0 + h) * D + x) =
+                    make_float4(acc.x / l, acc.y / l, acc.z / l, acc.w / l);
+            } else {
+                *reinterpret_cast<float4*>(pbase + h * D + x) = acc;
+            }
+        }
+        if (direct) continue;
+        // The chunk's maxima and row sums, once.
+        if (warp == 0 && lane < 8) {
+            float M = -INFINITY, l = 0.f;
+#pragma unroll
+            for (int w = 0; w < CW; w++) M = fmaxf(M, res_all[w * SM::res_floats + lane]);
+#pragma unroll
+            for (int w = 0; w < CW; w++) l = fmaf(res_all[w * SM::res_floats + 8 + lane], ex2(res_all[w * SM::res_floats + lane] - M), l);
+            pbase[8 * D + lane] = M;
+            pbase[8 * D + 8 + lane] = l;
+        }
+        // Hand the chunk to the epilogue warp and go on with the next item.
+        const uint32_t ms = kp % MAIL_SLOTS;
+        if (warp == 0) {
+            if (!__all_sync(0xffffffffu, mbar_wait(mfree0 + ms * 8, ((kp / MAIL_SLOTS) & 1) ^ 1))) {
+                *abort_flag = 1;  // seen by everyone at the next item's barrier
+            } else if (lane == 0) {
+                mailbox[ms].seq = it.seq; mailbox[ms].head0 = it.head0; mailbox[ms].nheads = it.nheads;
+                mailbox[ms].part0 = it.part0; mailbox[ms].nch = it.nch; mailbox[ms].counter = it.counter; mailbox[ms].stop = 0;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(mfull0 + ms * 8);
+        kp++;
+    }
+    // The end of the queue: tell the epilogue warp to finish what it holds and leave.
+    {
+        const uint32_t ms = kp % MAIL_SLOTS;
+        if (warp == 0) {
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(mfree0 + ms * 8, ((kp / MAIL_SLOTS) & 1) ^ 1));
+            if (ok && lane == 0) mailbox[ms].stop = 1;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(mfull0 + ms * 8);
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+extern int* device_status_word(qvx_device* dev);
+
+bool attn_stream_supported(const Layout& L, size_t heads) {
+    if (L.layout != QVX_LAYOUT_NATIVE || L.dtype == QVX_F32) return false;
+    if (L.B % TILE != 0 || heads % L.kvh != 0) return false;
+    return L.d == 64 || L.d == 128 || L.d == 256;
+}
+
+// Floats of scratch one partial result takes.
+size_t attn_stream_partial_floats(uint32_t d) { return 8 * (size_t)d + 16; }
+uint32_t attn_stream_counters_per_group() { return 1; }
+
+template <int DT, int D, bool PRECISE>
+static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t s) {
+    auto kernel = attn_stream_kernel<DT, D, PRECISE>;
+    static thread_local int ctas_per_sm = 0;
+    if (!ctas_per_sm) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamSmem<D>::total);
+        if (e == cudaSuccess)
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kernel, STREAM_THREADS, StreamSmem<D>::total);
+        if (e != cudaSuccess) { ctas_per_sm = 0; return check_cuda(dev, e, "streaming attention set-up"); }
+        if (ctas_per_sm < 1) ctas_per_sm = 1;
+    }
+    const unsigned grid = (unsigned)std::min<size_t>(a.n_items, (size_t)ctas_per_sm * dev->prop.multiProcessorCount);
+    kernel<<<grid, STREAM_THREADS, StreamSmem<D>::total, s>>>(a);
+    return check_cuda(dev, cudaGetLastError(), "streaming attention launch");
+}
+
+int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
+                           float* partials, uint32_t* counters, uint32_t* queue, cudaStream_t s) {
+    if (t->n_items == 0) return QVX_OK;
+    const Layout& L = t->L;
+    if (t->item_words > REC_WORDS)
+        return fail(dev, QVX_ERR_UNSUPPORTED, "streaming attention: %u blocks per chunk are too many", t->chunk_blocks);
+    if (((uintptr_t)q & 15u) || ((uintptr_t)out & 15u) || ((uintptr_t)pool & 127u))
+        return fail(dev, QVX_ERR_SHAPE,
+                    "shape mismatch in routed moe attention: q and out must be 16-byte aligned, the pool 128-byte aligned");
+    StreamArgs a;
+    a.pool = (const uint8_t*)pool; a.q = q; a.out = out; a.partials = partials; a.counters = counters; a.queue = queue;
+    a.items = t->d_items; a.status = device_status_word(dev);
+    a.block_bytes = L.block_bytes; a.page_bytes = L.page_bytes; a.tiles_per_block = L.B / TILE;
+    a.heads = (uint32_t)t->heads; a.item_words = t->item_words; a.n_items = (uint32_t)t->n_items;
+    a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;
+    static const bool one_pass = getenv("QVX_ATTN_ONE_PASS") != nullptr;  // experiments only
+    const bool precise = L.dtype == QVX_BF16 && !one_pass;
+    LaunchTimer timer(dev, QVX_K_ATTN, s);
+    int32_t rc = QVX_ERR_UNSUPPORTED;
+#define QVX_STREAM_CASE(TT, DD, PP) \
+    if (L.dtype == TT && L.d == DD && precise == PP) rc = launch_stream<TT, DD, PP>(dev, a, s);
+    QVX_STREAM_CASE(QVX_BF16, 64, true) QVX_STREAM_CASE(QVX_BF16, 128, true) QVX_STREAM_CASE(QVX_BF16, 256, true)
+    QVX_STREAM_CASE(QVX_BF16, 128, false)
+    QVX_STREAM_CASE(QVX_F16, 64, false) QVX_STREAM_CASE(QVX_F16, 128, false) QVX_STREAM_CASE(QVX_F16, 256, false)
+#undef QVX_STREAM_CASE
+    if (rc == QVX_ERR_UNSUPPORTED) return fail(dev, rc, "streaming attention: no kernel for this geometry");
+    return rc;
+}
+
+}  // namespace qvx

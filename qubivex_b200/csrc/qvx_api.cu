@@ -101,6 +101,7 @@ static int32_t check_status(qvx_device* dev) {
     if (dev->counters) {  // an item that gave up never arrived: start the counters from zero again
         cudaDeviceSynchronize();
         cudaMemset(dev->counters, 0, dev->counters_cap * 4);
+        if (dev->queue) cudaMemset(dev->queue, 0, 8);
     }
     return fail(dev, QVX_ERR_DEVICE, "cuda device error: a kernel gave up a bounded wait (status %d); its outputs are not valid", st);
 }
@@ -189,7 +190,7 @@ static uint32_t chunk_tokens_for(const Layout& L) {
     static const uint32_t configured = [] {
         const char* v = getenv("QVX_CHUNK_TOKENS");
         long n = v ? atol(v) : 0;
-        return (uint32_t)(n > 0 ? n : 256);
+        return (uint32_t)(n > 0 ? n : 512);
     }();
     uint32_t c = std::max(configured, L.B) / L.B * L.B;
     while (c > 2048 && c > L.B) c -= L.B;
@@ -242,7 +243,7 @@ static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint
         size_t nch = ((size_t)pos[t] + chunk) / chunk;
         im.max_nch = std::max<size_t>(im.max_nch, nch);
         im.n_items += nch * groups;
-        if (nch > 1) { im.n_parts += nch * groups; im.n_counters += groups; }
+        if (nch > 1) { im.n_parts += nch * groups; im.n_counters += groups * attn_counters_per_group(L); }
     }
     size_t off = 0;
     im.off_pos = off; off += 4 * s;
@@ -268,11 +269,12 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     std::vector<Key> keys;
     keys.reserve(im.n_items);
     std::vector<uint32_t> part_base(s), counter_base(s);
+    const uint32_t cpg = attn_counters_per_group(L);
     uint32_t part = 0, counter = 0;
     for (size_t t = 0; t < s; t++) {
         uint32_t len = pos[t] + 1u, nch = (len + chunk - 1) / chunk;
         part_base[t] = part; counter_base[t] = counter;
-        if (nch > 1) { part += nch * groups; counter += groups; }
+        if (nch > 1) { part += nch * groups; counter += groups * cpg; }
         for (uint32_t grp = 0; grp < groups; grp++)
             for (uint32_t c = 0; c < nch; c++) keys.push_back(Key{std::min(chunk, len - c * chunk), (uint32_t)t, grp, c});
     }
@@ -291,7 +293,7 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
         h.part0 = nch > 1 ? part_base[t] + k.grp * nch : 0xffffffffu;
         h.part = nch > 1 ? h.part0 + k.c : 0xffffffffu;
         h.nch = nch;
-        h.counter = nch > 1 ? counter_base[t] + k.grp : 0;
+        h.counter = nch > 1 ? counter_base[t] + k.grp * cpg : 0;  // the group's first arrival counter
         memcpy(w, &h, sizeof h);
         uint32_t count = (k.tokens + L.B - 1) / L.B;
         const uint32_t* src = blocks + table_at[t] + (size_t)k.c * im.chunk_blocks;
@@ -311,7 +313,7 @@ static void bind_image(qvx_tables* t, const TableImage& im, void* dmem) {
 }
 
 static int32_t ensure_partials(qvx_device* dev, size_t floats, size_t counters) {
-    if (floats * 4 <= dev->partials_cap && counters <= dev->counters_cap) return QVX_OK;
+    if (floats * 4 <= dev->partials_cap && counters <= dev->counters_cap && dev->queue) return QVX_OK;
     // Work queued earlier may still use the old scratch.
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return check_cuda(dev, e, "partials");
@@ -322,6 +324,11 @@ static int32_t ensure_partials(qvx_device* dev, size_t floats, size_t counters) 
         e = cudaMalloc(&dev->partials, cap);
         if (e != cudaSuccess) return check_cuda(dev, e, "partials");
         dev->partials_cap = cap;
+    }
+    if (!dev->queue) {
+        e = cudaMalloc((void**)&dev->queue, 8);
+        if (e == cudaSuccess) e = cudaMemset(dev->queue, 0, 8);
+        if (e != cudaSuccess) return check_cuda(dev, e, "work queue");
     }
     if (counters > dev->counters_cap) {
         if (dev->counters) cudaFree(dev->counters);
@@ -343,7 +350,7 @@ static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, c
     if (variant == QVX_ATTN_EXACT || !split_ok) return launch_attn_exact(dev, t, pool, q, out, s);
     int32_t rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
     if (rc) return rc;
-    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, dev->counters, s);
+    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, dev->counters, dev->queue, s);
 }
 
 }  // namespace qvx
@@ -421,6 +428,7 @@ void qvx_close(qvx_device* dev) {
     for (cudaEvent_t ev : dev->event_pool) cudaEventDestroy(ev);
     if (dev->partials) cudaFree(dev->partials);
     if (dev->counters) cudaFree(dev->counters);
+    if (dev->queue) cudaFree(dev->queue);
     if (dev->staging) cudaFreeHost(dev->staging);
     if (dev->dstaging) cudaFree(dev->dstaging);
     DeviceExtras* x = nullptr;

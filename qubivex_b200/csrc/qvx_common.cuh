@@ -149,6 +149,7 @@ struct qvx_device {
     size_t partials_cap = 0;
     uint32_t* counters = nullptr;
     size_t counters_cap = 0;
+    uint32_t* queue = nullptr;  // the streaming kernel's work queue: next item, CTAs done
     // Pinned staging for the _host calls, grown on demand; `staging_used` is reset by qvx_wait.
     char* staging = nullptr;
     size_t staging_cap = 0, staging_used = 0;
@@ -213,9 +214,10 @@ struct qvx_tables {
 
 namespace qvx {
 int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                          float* partials, uint32_t* counters, cudaStream_t s);
+                          float* partials, uint32_t* counters, uint32_t* queue, cudaStream_t s);
 int32_t launch_attn_exact(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                           cudaStream_t s);
 size_t attn_partial_floats(const qvx_tables* t);  // floats of scratch the split kernel needs
 bool attn_split_supported(const Layout& L, size_t heads);
+uint32_t attn_counters_per_group(const Layout& L);
 }  // namespace qvx
