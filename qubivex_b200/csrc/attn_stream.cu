@@ -316,6 +316,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             it.part = rec[4]; it.part0 = rec[5]; it.nch = rec[6]; it.counter = rec[7];
             if (it.tokens == 0) break;  // the end of the queue: every consumer warp reads the same record
         }
+        // The warp that takes the item's tiles 0, CW, 2 CW, ...: the merge below goes through the
+        // warps in the order of the tiles they took, so that the sum order does not depend on
+        // how many tiles this CTA happened to stream before the item.
+        const uint32_t rot = (CW - nbase % CW) % CW;
         float o[D / 16][4];
 #pragma unroll
         for (int m = 0; m < D / 16; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; }
@@ -449,8 +453,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             float l = 0.f;
 #pragma unroll
-            for (int w = 0; w < CW; w++) {
-                const float* r = res_all + w * SM::res_floats;
+            for (int c = 0; c < CW; c++) {
+                const float* r = res_all + ((c + rot) % CW) * SM::res_floats;
                 const float wg = ex2(r[h] - M);
                 const float4 v = *reinterpret_cast<const float4*>(r + 16 + h * D + x);
                 acc.x = fmaf(v.x, wg, acc.x); acc.y = fmaf(v.y, wg, acc.y);
@@ -471,7 +475,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
 #pragma unroll
             for (int w = 0; w < CW; w++) M = fmaxf(M, res_all[w * SM::res_floats + lane]);
 #pragma unroll
-            for (int w = 0; w < CW; w++) l = fmaf(res_all[w * SM::res_floats + 8 + lane], ex2(res_all[w * SM::res_floats + lane] - M), l);
+            for (int c = 0; c < CW; c++) {
+                const float* r = res_all + ((c + rot) % CW) * SM::res_floats;
+                l = fmaf(r[8 + lane], ex2(r[lane] - M), l);
+            }
             pbase[8 * D + lane] = M;
             pbase[8 * D + 8 + lane] = l;
         }
