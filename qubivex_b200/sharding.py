@@ -1,0 +1,76 @@
+"""How the path is divided over the GPUs of one box: by sequence, or by KV head.
+
+Attention of one (token, head) needs nothing from any other (crates/qubivex-arch/src/lib.rs:1304-1306),
+and a GQA group shares its keys and values with no other group, so neither division puts a
+collective inside the path.  Sharding by KV head needs one exchange after it: every rank holds
+[token][its heads][d] and the caller wants [token][head][d] — an all-gather and a transpose.
+The reference has a single device (crates/qubivex-runtime/src/engine.rs:1290); this is new.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+
+def sequence_shard(n_sequences: int, rank: int, world: int) -> range:
+    """The sequences rank `rank` owns: contiguous, sizes differing by at most one."""
+    base, extra = divmod(n_sequences, world)
+    lo = rank * base + min(rank, extra)
+    return range(lo, lo + base + (1 if rank < extra else 0))
+
+
+@dataclass(frozen=True)
+class HeadShard:
+    """Rank `rank` owns `kv_heads` KV heads starting at `kv0`, and the query heads of their groups."""
+    rank: int
+    world: int
+    kv0: int
+    kv_heads: int
+    head0: int
+    heads: int
+    head_dim: int
+
+    def q(self, q: np.ndarray) -> np.ndarray:
+        """[token][head][d] -> this rank's [token][local head][d], contiguous."""
+        return np.ascontiguousarray(q[:, self.head0:self.head0 + self.heads, :])
+
+    def kv_rows(self, rows: np.ndarray, total_kv_heads: int) -> np.ndarray:
+        """[row][kv_out] -> this rank's [row][local kv_out] (key rows, value rows, k_new, v_new)."""
+        r = rows.reshape(rows.shape[0], total_kv_heads, self.head_dim)
+        return np.ascontiguousarray(r[:, self.kv0:self.kv0 + self.kv_heads, :]).reshape(rows.shape[0], -1)
+
+    def sync_rows(self, sync: np.ndarray, total_kv_heads: int) -> np.ndarray:
+        """[row][key row | value row] -> the same for this rank's KV heads."""
+        kv_out = total_kv_heads * self.head_dim
+        k, v = sync[:, :kv_out], sync[:, kv_out:]
+        return np.ascontiguousarray(np.concatenate([self.kv_rows(k, total_kv_heads), self.kv_rows(v, total_kv_heads)], axis=1))
+
+
+def head_shard(heads: int, kv_heads: int, head_dim: int, rank: int, world: int) -> HeadShard:
+    if kv_heads % world != 0:
+        raise ValueError(f"{kv_heads} KV heads do not divide over {world} ranks")
+    per = kv_heads // world
+    group = heads // kv_heads
+    return HeadShard(rank, world, rank * per, per, rank * per * group, per * group, head_dim)
+
+
+def merge_heads(gathered) -> np.ndarray:
+    """[rank][token][local head][d] (what an all-gather leaves) -> [token][head][d]."""
+    g = np.asarray(gathered)
+    world, s, hl, d = g.shape
+    return np.ascontiguousarray(g.transpose(1, 0, 2, 3).reshape(s, world * hl, d))
+
+
+def all_gather_heads(out_local, group=None):
+    """The one exchange of the head-sharded path: torch.distributed all-gather of this rank's
+    [token][local head][d] tensor (NCCL over NVLink on GPUs, gloo on CPU ranks), then the
+    transpose to [token][head][d].  Every rank gets the whole result."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    gathered = torch.empty((world,) + tuple(out_local.shape), dtype=out_local.dtype, device=out_local.device)
+    dist.all_gather(list(gathered.unbind(0)), out_local.contiguous(), group=group)
+    s, hl, d = out_local.shape
+    return gathered.permute(1, 0, 2, 3).reshape(s, world * hl, d).contiguous()

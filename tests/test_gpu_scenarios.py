@@ -1,0 +1,258 @@
+"""The path end to end on a B200, as the reference's runtime drives it: the pool and its block
+tables (OnDevice), host rows synced once, decode steps, prefix sharing with copy-on-write,
+compaction.  Every step is checked against the CPU oracle fed the same tables: attention per
+step, pool bytes at the end.  Shapes follow the benchmark configurations, scaled to seconds."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import within
+from qubivex_b200 import device as qd
+from qubivex_b200.ondevice import AttnSeq, OnDevice
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f32": 0, "bf16": 1}
+
+
+class HostCache:
+    """The authoritative host copy of one sequence's keys and values: [kv_head][position][d]
+    (KvCache, crates/qubivex-arch/src/lib.rs:283-524)."""
+
+    def __init__(self, kvh, d, cap, rng, scale=1.0):
+        self.k = (rng.standard_normal((kvh, cap, d), dtype=np.float32) * scale).astype(np.float32)
+        self.v = (rng.standard_normal((kvh, cap, d), dtype=np.float32) * scale).astype(np.float32)
+        self.len = 0
+        self.epoch = 0
+
+    def row(self, p):
+        return self.k[:, p, :].reshape(-1), self.v[:, p, :].reshape(-1)
+
+
+def oracle_step(pool, geo_o, heads, plan, seqs, q, k_new, v_new):
+    """The same op on the CPU: the copies copy-on-write asked for, then sync rows, new rows, attention."""
+    if len(plan.copy_src):
+        assert oracle.block_copy(pool, geo_o, plan.copy_src, plan.copy_dst) == 0
+    kv_out = geo_o.kv_heads * geo_o.head_dim
+    sync = np.empty((len(plan.sync_to), 2 * kv_out), dtype=np.float32)
+    for r, (si, p) in enumerate(zip(plan.sync_seq, plan.sync_pos)):
+        sync[r, :kv_out], sync[r, kv_out:] = seqs[int(si)].host.row(int(p))
+    rc, att = oracle.paged_attention(pool, geo_o, heads, q, k_new, v_new, plan.pos, plan.blocks, plan.table_at, sync, plan.sync_to)
+    assert rc == 0
+    return att
+
+
+class Seq:
+    def __init__(self, host):
+        self.host = host
+        self.mirror = None
+
+    def attn_seq(self):
+        return AttnSeq(self.mirror, self.host.k, self.host.v, self.host.len, self.host.epoch)
+
+
+def decode_step(od, seqs, pool_o, geo_o, heads, rng, dtype, variant, scale=1.0, layer=0):
+    """One decode pass over `seqs` at their current lengths: device and oracle, compared."""
+    s = len(seqs)
+    kvh, d = geo_o.kv_heads, geo_o.head_dim
+    q = (rng.standard_normal((s, heads, d), dtype=np.float32) * scale).astype(np.float32)
+    k_new = np.stack([sq.host.row(sq.host.len)[0] for sq in seqs])
+    v_new = np.stack([sq.host.row(sq.host.len)[1] for sq in seqs])
+    aseqs = [sq.attn_seq() for sq in seqs]
+    out = od.attention(aseqs, layer, q, k_new, v_new, variant=variant)
+    assert out is not None
+    for sq, a in zip(seqs, aseqs):
+        sq.mirror = a.mirror
+    want = oracle_step(pool_o, geo_o, heads, od.last_plan, seqs, q, k_new, v_new)
+    for sq in seqs:
+        sq.host.len += 1
+    if variant == qd.ATTN_EXACT and dtype == "f32":
+        assert np.array_equal(out.view(np.uint32), want.view(np.uint32))
+    else:
+        ok, err = within(out, want, dtype)
+        assert ok, err
+    return od.last_plan
+
+
+def read_pool(dev, od, n_bytes):
+    return dev.read(od.kv_buffer(), 0, n_bytes)
+
+
+# ---- C1: the reference-runnable configuration ---------------------------------------------------
+@pytest.mark.parametrize("variant", [qd.ATTN_EXACT, qd.ATTN_SPLIT])
+def test_c1_prompts_then_64_decode_steps(dev, variant):
+    """1 layer, block 16, f32, 8 q / 2 kv heads of 64; prompts 37/128/255/512; 64 decode steps; the
+    256-block pool handed out in a seeded random permutation.  Outputs: attention per step and
+    the final pool bytes."""
+    heads, kvh, d, B, blocks = 8, 2, 64, 16, 256
+    geo_d, geo_o = qd.geometry(B, kvh, d, qd.F32), oracle.geometry(B, kvh, d, oracle.F32)
+    rng = np.random.default_rng(20261125)
+    od = OnDevice(dev, geo_d, heads, blocks=blocks)
+    od.kv.set_free_order(rng.permutation(blocks))
+    n_bytes = blocks * oracle.block_bytes(geo_o)
+    dev.write(od.kv_buffer(), 0, np.zeros(n_bytes, dtype=np.uint8))
+    pool_o = np.zeros(n_bytes, dtype=np.uint8)
+    seqs = []
+    for n in (37, 128, 255, 512):
+        sq = Seq(HostCache(kvh, d, n + 64, rng))
+        sq.host.len = n          # the prompt was run on the host: its rows reach the pool by sync
+        seqs.append(sq)
+    first = decode_step(od, seqs, pool_o, geo_o, heads, rng, "f32", variant)
+    assert len(first.sync_to) == 37 + 128 + 255 + 512          # every prompt row synced exactly once
+    for _ in range(63):
+        plan = decode_step(od, seqs, pool_o, geo_o, heads, rng, "f32", variant)
+        assert len(plan.sync_to) == 0
+    assert np.array_equal(read_pool(dev, od, n_bytes), pool_o)
+    st = od.kv.stats()
+    assert st.synced_rows == 932 and st.layers == 64 and st.full == 0
+    for sq in seqs:
+        sq.mirror.drop()
+    assert od.kv.stats().free == blocks                         # tests/discrete.rs:724-727
+    od.close()
+
+
+# ---- the host cache stays authoritative ----------------------------------------------------------
+def test_a_cleared_cache_and_a_failed_pass_are_resynced(dev):
+    heads, kvh, d, B = 8, 2, 64, 16
+    geo_d, geo_o = qd.geometry(B, kvh, d, qd.BF16), oracle.geometry(B, kvh, d, oracle.BF16)
+    rng = np.random.default_rng(3)
+    od = OnDevice(dev, geo_d, heads, blocks=32)
+    n_bytes = 32 * oracle.block_bytes(geo_o)
+    dev.write(od.kv_buffer(), 0, np.zeros(n_bytes, dtype=np.uint8))
+    pool_o = np.zeros(n_bytes, dtype=np.uint8)
+    sq = Seq(HostCache(kvh, d, 200, rng))
+    sq.host.len = 50
+    decode_step(od, [sq], pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT)
+    # a pass that failed after the device stored its row: the host is back at 49 positions
+    sq.host.len = 49
+    sq.host.k[:, 49:, :] += 1.0
+    plan = decode_step(od, [sq], pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT)
+    assert len(plan.sync_to) == 0 and int(plan.pos[0]) == 49    # the new row rewrites position 49
+    # the cache was cleared and another prompt run: a new epoch starts the mirror again
+    sq.host = HostCache(kvh, d, 200, rng)
+    sq.host.len, sq.host.epoch = 20, 1
+    plan = decode_step(od, [sq], pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT)
+    assert len(plan.sync_to) == 20
+    assert np.array_equal(read_pool(dev, od, n_bytes), pool_o)
+    sq.mirror.drop()
+    od.close()
+
+
+def test_a_pool_one_block_short_declines_and_counts_it(dev):
+    # crates/qubivex-runtime/tests/discrete.rs:735-767
+    heads, kvh, d, B = 8, 2, 64, 16
+    od = OnDevice(dev, qd.geometry(B, kvh, d, qd.BF16), heads, blocks=3)
+    rng = np.random.default_rng(4)
+    a, b = Seq(HostCache(kvh, d, 64, rng)), Seq(HostCache(kvh, d, 64, rng))
+    a.host.len = b.host.len = 31
+    aseqs = [a.attn_seq(), b.attn_seq()]
+    q = rng.standard_normal((2, heads, d), dtype=np.float32)
+    kv = rng.standard_normal((2, kvh * d), dtype=np.float32)
+    assert od.attention(aseqs, 0, q, kv, kv) is None            # declined: the host runs this layer
+    assert od.kv.stats().full == 1 and od.routed == 0
+    for s_ in aseqs:
+        s_.mirror.drop()
+    od.close()
+
+
+# ---- C3: a shared prefix, copy-on-write on the first divergent append ------------------------------
+@pytest.mark.parametrize("prefix,copies", [(8 * 16 + 8, 3), (8 * 16, 0)])
+def test_c3_shared_prefix_and_copy_on_write(dev, prefix, copies):
+    """Three of four sequences share a prefix through reference-counted blocks.  A prefix that
+    ends inside a block forces one whole-block copy per sharer on its first append (the retained
+    prefix holds the block too, so nobody writes in place); one that ends on a block boundary
+    copies nothing."""
+    heads, kvh, d, B, blocks = 32, 4, 128, 16, 160
+    geo_d, geo_o = qd.geometry(B, kvh, d, qd.BF16), oracle.geometry(B, kvh, d, oracle.BF16)
+    rng = np.random.default_rng(33)
+    scale = d ** -0.5
+    od = OnDevice(dev, geo_d, heads, blocks=blocks)
+    od.kv.set_free_order(rng.permutation(blocks))
+    n_bytes = blocks * oracle.block_bytes(geo_o)
+    dev.write(od.kv_buffer(), 0, np.zeros(n_bytes, dtype=np.uint8))
+    pool_o = np.zeros(n_bytes, dtype=np.uint8)
+    # the retained value: a sequence that ran the prefix and stays in the index
+    owner = Seq(HostCache(kvh, d, prefix + 8, rng, scale))
+    owner.host.len = prefix - 1
+    decode_step(od, [owner], pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT, scale)   # pool now holds 0..prefix-1
+    assert owner.mirror.synced(0) == prefix
+    sharers = []
+    for _ in range(3):
+        sq = Seq(HostCache(kvh, d, 600, rng, scale))
+        sq.host.k[:, :prefix] = owner.host.k[:, :prefix]           # the same tokens: the same keys and values
+        sq.host.v[:, :prefix] = owner.host.v[:, :prefix]
+        sq.host.len = prefix
+        sq.mirror = owner.mirror.fork(prefix)                      # a table copy and reference counts, no bytes
+        sharers.append(sq)
+    lone = Seq(HostCache(kvh, d, 600, rng, scale))
+    lone.host.len = 300
+    free_before = od.kv.stats().free
+    plan = decode_step(od, sharers + [lone], pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT, scale)
+    assert len(plan.copy_src) == copies and od.kv.stats().cow_copies == copies
+    assert len(plan.sync_to) == 300                                # only the lone sequence's prompt
+    shared_blocks = prefix // B
+    for sq in sharers:
+        assert sq.mirror.blocks(0)[:shared_blocks].tolist() == owner.mirror.blocks(0)[:shared_blocks].tolist()
+    assert od.kv.refcount(int(owner.mirror.blocks(0)[0])) == 4
+    new_blocks = (300 // B + 1) + 3                                 # lone's table + one block per sharer (copy or growth)
+    assert free_before - od.kv.stats().free == new_blocks
+    for _ in range(20):
+        plan = decode_step(od, sharers + [lone], pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT, scale)
+        assert len(plan.copy_src) == 0
+    assert np.array_equal(read_pool(dev, od, n_bytes), pool_o)
+    for sq in sharers + [lone, owner]:
+        sq.mirror.drop()
+    assert od.kv.stats().free == blocks
+    od.close()
+
+
+# ---- C4: churn, compaction, then attention ---------------------------------------------------------
+def test_c4_churn_compaction_then_attention(dev):
+    """32 q / 8 kv heads of 128, bf16, block 32.  Sequences retire and arrive at random; a compaction
+    pass gathers the live blocks to the front of the pool (moves on the device, tables rewritten
+    on the host); one decode step over every live sequence follows.  The live prefix of the pool
+    and the attention outputs must match the oracle's."""
+    heads, kvh, d, B, blocks = 32, 8, 128, 32, 96
+    geo_d, geo_o = qd.geometry(B, kvh, d, qd.BF16), oracle.geometry(B, kvh, d, oracle.BF16)
+    bb = oracle.block_bytes(geo_o)
+    rng = np.random.default_rng(44)
+    scale = d ** -0.5
+    od = OnDevice(dev, geo_d, heads, blocks=blocks)
+    od.kv.set_free_order(rng.permutation(blocks))
+    n_bytes = blocks * bb
+    dev.write(od.kv_buffer(), 0, np.zeros(n_bytes, dtype=np.uint8))
+    pool_o = np.zeros(n_bytes, dtype=np.uint8)
+
+    def admit():
+        sq = Seq(HostCache(kvh, d, 700, rng, scale))
+        sq.host.len = int(rng.integers(40, 250))
+        return sq
+
+    live = [admit() for _ in range(6)]
+    decode_step(od, live, pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT, scale)
+    moved = 0
+    for step in range(6):
+        # retire a third, admit as many
+        for _ in range(2):
+            sq = live.pop(int(rng.integers(0, len(live))))
+            sq.mirror.drop()
+        fresh = [admit(), admit()]
+        live += fresh
+        decode_step(od, live, pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT, scale)
+        src, dst = od.kv.compact()
+        L = int(od.kv.stats().blocks - od.kv.stats().free)
+        assert np.all(src >= L) and np.all(dst < L) and len(set(dst.tolist())) == len(dst)
+        dev.block_copy(od.kv_buffer(), geo_d, src, dst)
+        assert oracle.block_copy(pool_o, geo_o, src, dst) == 0
+        moved += len(src)
+        for sq in live:
+            assert np.all(sq.mirror.blocks(0) < L)                 # every live block is in the prefix now
+        decode_step(od, live, pool_o, geo_o, heads, rng, "bf16", qd.ATTN_SPLIT, scale)
+        got = read_pool(dev, od, n_bytes)
+        L = int(od.kv.stats().blocks - od.kv.stats().free)
+        assert np.array_equal(got[: L * bb], pool_o[: L * bb])
+    assert moved > 0 and od.kv.stats().compaction_moves == moved
+    for sq in live:
+        sq.mirror.drop()
+    assert od.kv.stats().free == blocks
+    od.close()
