@@ -170,6 +170,27 @@ const uint32_t *qvx_tables_table_at(qvx_tables *t);
 int32_t qvx_attn_decode(qvx_device *dev, qvx_tables *tables, const void *pool, const float *q,
                         float *out, uint32_t variant, void *stream);
 
+/* Paged decode attention for a caller that must not allocate device memory.  It has no
+ * counterpart in the reference.  qubivex's runtime charges every device byte to a ledger and
+ * gives the KV pool whatever the budget leaves, so a host that has committed the whole device
+ * cannot have its backend call cudaMalloc later (it can fail, it is outside the ledger, and
+ * cudaMalloc / cudaFree stall every stream in the middle of a decode step).  qvx_attn_decode
+ * grows its scratch on demand and needs a qvx_tables object; this call needs neither: pos,
+ * blocks and table_at are the caller's own device arrays (unchecked: a block id past the pool
+ * is the caller's fault, as with qvx_kv_append), max_pos is a bound on pos[] the host knows
+ * (a position beyond it is refused through the device status, nothing written for it), and
+ * the scratch is a fixed array inside the library: 16 MiB of partial results + 16384
+ * arrival counters, held on every GPU that loads the library until the process exits.
+ * An op that needs more ((sequences x head groups) > 16384, or
+ * sequences x head groups x ceil((max_pos + 1) / 512) x (8 * head_dim + 16) x 4 bytes > 16 MiB)
+ * returns QVX_ERR_UNSUPPORTED with the sizes in qvx_last_error.  bf16 or f16 pools in the native
+ * layout, head_dim 64 or 128.  The first call on a device looks the array's address up: make
+ * that call outside any stream capture.  All calls share the array: calls that overlap on
+ * the GPU race on it, so keep them on one stream or order them. */
+int32_t qvx_attn_decode_static(qvx_device *dev, const qvx_geometry *geo, const void *pool, size_t heads,
+                               size_t s, const float *q, const uint32_t *pos, const uint32_t *blocks,
+                               const uint32_t *table_at, uint32_t max_pos, float *out, void *stream);
+
 /* Whole-block copies src[i] -> dst[i]: the copy of a shared block before the first
  * divergent append, and the moves of a compaction pass.  No counterpart in the reference,
  * which copies a whole cache (crates/qubivex-arch/src/lib.rs:409-432) and never moves a

@@ -31,6 +31,7 @@ SOURCES = {
     "block_copy.cu": [],
     "attn_split.cu": [],
     "attn_stream.cu": [],
+    "attn_static.cu": [],
     "attn_exact.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],
     "runtime.cpp": [],
 }

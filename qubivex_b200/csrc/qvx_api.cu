@@ -103,7 +103,8 @@ static int32_t check_status(qvx_device* dev) {
         cudaMemset(dev->counters, 0, dev->counters_cap * 4);
         if (dev->queue) cudaMemset(dev->queue, 0, 8);
     }
-    return fail(dev, QVX_ERR_DEVICE, "cuda device error: a kernel gave up a bounded wait (status %d); its outputs are not valid", st);
+    return fail(dev, QVX_ERR_DEVICE, "cuda device error: %s (status %d); the op's outputs are not valid",
+                st == 2 ? "a position beyond the bound the caller gave" : "a kernel gave up a bounded wait", st);
 }
 
 // ---- capacity accounting, as SimDevice::reserve (sim.rs:176-203) -----------------------------
