@@ -76,7 +76,7 @@ typedef struct qvx_config {
     int32_t device;     /* CUDA ordinal                                                   */
     uint64_t capacity;  /* bytes alloc/upload may hold in all; 0 = the device's free memory */
     uint64_t kv_pool;   /* DiscreteDevice::kv_pool(); 0 = None (the runtime's default)     */
-    uint32_t timing;    /* 1: time every kernel launch with CUDA events (TransferStats.timed) */
+    uint32_t timing;    /* n > 0: time every n-th launch of each kernel with CUDA events (TransferStats.timed) */
 } qvx_config;
 
 int32_t qvx_open(const qvx_config *cfg, qvx_device **dev);
@@ -169,6 +169,14 @@ const uint32_t *qvx_tables_table_at(qvx_tables *t);
  * h / (heads / kv_heads). */
 int32_t qvx_attn_decode(qvx_device *dev, qvx_tables *tables, const void *pool, const float *q,
                         float *out, uint32_t variant, void *stream);
+
+/* The two stages of a decode step in the reference's order — each token's new row stored at
+ * pos[t], then attention over 0..=pos[t] (crates/qubivex-backend-cpu/src/sim.rs:394-429;
+ * `attn_prelude.comp` then `attn_decode.comp`) — as one call.  On 16-bit native pools the rows are
+ * stored inside the attention launch (by the CTA that reads them); otherwise this is
+ * qvx_kv_append followed by qvx_attn_decode.  k_new, v_new: s x kv_out f32. */
+int32_t qvx_kv_append_attn_decode(qvx_device *dev, qvx_tables *tables, void *pool, const float *k_new,
+                                  const float *v_new, const float *q, float *out, uint32_t variant, void *stream);
 
 /* Paged decode attention for a caller that must not allocate device memory.  It has no
  * counterpart in the reference.  qubivex's runtime charges every device byte to a ledger and

@@ -92,6 +92,7 @@ PROTOTYPES = {
     "qvx_tables_blocks": (P, [P]),
     "qvx_tables_table_at": (P, [P]),
     "qvx_attn_decode": (C.c_int32, [P, P, P, P, P, C.c_uint32, P]),
+    "qvx_kv_append_attn_decode": (C.c_int32, [P, P, P, P, P, P, P, C.c_uint32, P]),
     "qvx_attn_decode_static": (C.c_int32, [P, _GEO, P, C.c_size_t, C.c_size_t, P, P, P, P, C.c_uint32, P, P]),
     "qvx_block_copy": (C.c_int32, [P, _GEO, P, C.c_size_t, P, P, C.c_size_t, P]),
     "qvx_paged_attention_host": (C.c_int32, [P, P, _GEO, C.c_size_t, C.c_size_t, P, P, P, P, P, C.c_size_t, P, P, P,

@@ -11,6 +11,8 @@
 //   - CTAs are persistent.  Each takes work items (a chunk of one sequence for one kv head
 //     and its group of <= 8 query heads) from a device-wide queue, longest first, until
 //     the queue is empty; a CTA never waits for another CTA.
+//   - The step's KV append can ride in the same launch: the producer warp of the CTA that takes
+//     a sequence's last chunk stores the new key and value rows of its KV head first.
 //   - One producer warp per CTA walks the queue one item ahead of its own copies: the next
 //     item's index (an atomic) and record (header + block ids, one bulk copy) are in flight
 //     while it issues the current item's tiles.  For every tile of 16 positions it issues bulk
@@ -59,8 +61,10 @@ struct StreamArgs {
     uint32_t* queue;        // [0] next item, [1] CTAs done; both zero between launches
     const uint32_t* items;
     int* status;
+    const float* k_new;     // the step's new rows, s x kv_out f32 each, stored by this launch; or null
+    const float* v_new;
     uint64_t block_bytes;
-    uint32_t page_bytes, tiles_per_block, heads, item_words, n_items;
+    uint32_t page_bytes, tiles_per_block, heads, item_words, n_items, kv_out;
     float scale_log2;
 };
 
@@ -201,8 +205,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
 
     if (warp == CW) {
         // ================================ producer ================================
-        // Only lane 0 works; the other lanes leave at once.
-        if (lane != 0) return;
+        // Lane 0 walks the queue and issues every copy; the whole warp meets once per item, to
+        // store the sequence's new key and value rows when the item holds its last position.
         uint32_t* rec_base = reinterpret_cast<uint32_t*>(smem + SM::rec_off);
         const uint32_t rec_bytes_one = a.item_words * 4;
         // Fetches item `idx` into record slot j % REC_SLOTS (or writes the end-of-queue record).
@@ -218,58 +222,94 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
         };
         uint32_t n = 0;          // tiles issued so far, over all items
-        bool failed = false;
-        uint32_t idx_next = atomicAdd(a.queue, 1u);
-        fetch(0, idx_next);
-        bool queue_dry = idx_next >= a.n_items;
-        idx_next = queue_dry ? idx_next : atomicAdd(a.queue, 1u);  // item 1: in flight while item 0 is set up
+        bool failed = false, queue_dry = false;
+        uint32_t idx_next = 0;
+        if (lane == 0) {
+            // The first item needs no atomic: CTA b starts with item b, the queue hands out the rest.
+            idx_next = blockIdx.x;
+            fetch(0, idx_next);
+            idx_next = gridDim.x + atomicAdd(a.queue, 1u);  // item 1: in flight while item 0 is set up
+        }
         for (uint32_t k = 0;; k++) {
             const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
-            if (!mbar_wait(recbar0 + rslot * 8, (k / REC_SLOTS) & 1)) { failed = true; break; }
-            const uint32_t* rec = rec_base + rslot * REC_WORDS;
-            const uint32_t seq = rec[0], tokens = rec[1], head0 = rec[2], nheads = rec[3] & 0xffffu, kvh = rec[3] >> 16;
             // The consumers are done with the queries of item k - Q_SLOTS (and so with every
             // record before it).
-            if (!mbar_wait(qempty0 + qslot * 8, ((k / Q_SLOTS) & 1) ^ 1)) { failed = true; break; }
+            bool ok = mbar_wait(recbar0 + rslot * 8, (k / REC_SLOTS) & 1);
+            ok = ok && mbar_wait(qempty0 + qslot * 8, ((k / Q_SLOTS) & 1) ^ 1);
+            if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
+            const uint32_t* rec = rec_base + rslot * REC_WORDS;
+            const uint32_t seq = rec[0], tokens = rec[1], head0 = rec[2], nheads = rec[3] & 0xffffu, kvh = rec[3] >> 16;
             if (tokens == 0) {
-                mbar_arrive(qfull0 + qslot * 8);  // hand the end-of-queue record to the consumers
+                if (lane == 0) mbar_arrive(qfull0 + qslot * 8);  // hand the end-of-queue record to the consumers
                 break;
             }
-            mbar_expect_tx(qfull0 + qslot * 8, nheads * D * 4);
-            const float* qp = a.q + ((size_t)seq * a.heads + head0) * D;
-            for (uint32_t h = 0; h < nheads; h++)
-                bulk_g2s(sbase + SM::q_off + (qslot * 8 + h) * SM::q_stride, qp + (size_t)h * D, D * 4, qfull0 + qslot * 8);
-            // Item k + 1: its index has had a whole item's time to come back.
-            fetch(k + 1, idx_next);
-            if (!queue_dry) {
-                queue_dry = idx_next >= a.n_items;
-                if (!queue_dry) idx_next = atomicAdd(a.queue, 1u);
-            }
-            const uint32_t ntiles = (tokens + TILE - 1) / TILE;
             const uint8_t* base = a.pool + (uint64_t)kvh * 2u * a.page_bytes;
-            for (uint32_t tau = 0; tau < ntiles; tau++, n++) {
-                const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
-                if (!mbar_wait(empty0 + st * 8, ph ^ 1)) { failed = true; break; }
-                const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + tau / a.tiles_per_block];
-                const uint8_t* src = base + (uint64_t)blk * a.block_bytes + (uint64_t)(tau % a.tiles_per_block) * SM::tile_bytes;
-                const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
-                mbar_expect_tx(full0 + st * 8, SM::stage_bytes);
-                if (a.page_bytes == SM::tile_bytes) {  // one tile per block: its values follow its keys
-                    bulk_g2s(dst, src, SM::stage_bytes, full0 + st * 8);
-                } else {
-                    bulk_g2s(dst, src, SM::tile_bytes, full0 + st * 8);
-                    bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, full0 + st * 8);
+            if (a.k_new != nullptr) {
+                // KV append fused in: the chunk that ends the sequence holds the position the step
+                // adds.  Its rows go into the pool now, long before the tile that reads them is
+                // asked for (sim.rs:394-398: the new row is stored, then attention reads 0..=pos).
+                const uint32_t part = rec[4], part0 = rec[5], nch = rec[6];
+                const bool last_chunk = part == NO_PART || part - part0 == nch - 1;
+                if (last_chunk) {
+                    const uint32_t p = tokens - 1, B = a.tiles_per_block * TILE, slot = p % B;
+                    const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + p / B];
+                    uint8_t* row = const_cast<uint8_t*>(base) + (uint64_t)blk * a.block_bytes + (uint64_t)slot * (D * 2);
+                    constexpr uint32_t CPR = D * 2 / 16;  // 16-byte chunks per row
+                    for (uint32_t i = lane; i < 2 * CPR; i += 32) {
+                        const uint32_t kv = i / CPR, c = i % CPR;
+                        const float* src = (kv ? a.v_new : a.k_new) + (size_t)seq * a.kv_out + kvh * D + c * 8;
+                        const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+                        uint4 w;
+                        w.x = (uint32_t)narrow16(lo.x, DT) | ((uint32_t)narrow16(lo.y, DT) << 16);
+                        w.y = (uint32_t)narrow16(lo.z, DT) | ((uint32_t)narrow16(lo.w, DT) << 16);
+                        w.z = (uint32_t)narrow16(hi.x, DT) | ((uint32_t)narrow16(hi.y, DT) << 16);
+                        w.w = (uint32_t)narrow16(hi.z, DT) | ((uint32_t)narrow16(hi.w, DT) << 16);
+                        *reinterpret_cast<uint4*>(row + (uint64_t)kv * a.page_bytes + ((c ^ (slot & 7u)) << 4)) = w;
+                    }
+                    __threadfence();  // the rows are in device memory ...
+                    asm volatile("fence.proxy.async.global;" ::: "memory");  // ... before any bulk copy reads them
+                }
+                __syncwarp();
+            }
+            if (lane == 0) {
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                mbar_expect_tx(qfull0 + qslot * 8, nheads * D * 4);
+                const float* qp = a.q + ((size_t)seq * a.heads + head0) * D;
+                for (uint32_t h = 0; h < nheads; h++)
+                    bulk_g2s(sbase + SM::q_off + (qslot * 8 + h) * SM::q_stride, qp + (size_t)h * D, D * 4, qfull0 + qslot * 8);
+                // Item k + 1: its index has had a whole item's time to come back.
+                fetch(k + 1, idx_next);
+                if (!queue_dry) {
+                    queue_dry = idx_next >= a.n_items;
+                    if (!queue_dry) idx_next = gridDim.x + atomicAdd(a.queue, 1u);
+                }
+                const uint32_t ntiles = (tokens + TILE - 1) / TILE;
+                for (uint32_t tau = 0; tau < ntiles; tau++, n++) {
+                    const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
+                    if (!mbar_wait(empty0 + st * 8, ph ^ 1)) { failed = true; break; }
+                    const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + tau / a.tiles_per_block];
+                    const uint8_t* src = base + (uint64_t)blk * a.block_bytes + (uint64_t)(tau % a.tiles_per_block) * SM::tile_bytes;
+                    const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
+                    mbar_expect_tx(full0 + st * 8, SM::stage_bytes);
+                    if (a.page_bytes == SM::tile_bytes) {  // one tile per block: its values follow its keys
+                        bulk_g2s(dst, src, SM::stage_bytes, full0 + st * 8);
+                    } else {
+                        bulk_g2s(dst, src, SM::tile_bytes, full0 + st * 8);
+                        bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, full0 + st * 8);
+                    }
                 }
             }
-            if (failed) break;
+            if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
         }
-        if (failed) {
-            *abort_flag = 1;
-            atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+        if (lane == 0) {
+            if (failed) {
+                *abort_flag = 1;
+                atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+            }
+            // The last CTA to run out of work leaves the queue ready for the next launch.
+            const uint32_t done = atomicAdd(a.queue + 1, 1u);
+            if (done == gridDim.x - 1) { a.queue[0] = 0; a.queue[1] = 0; }
         }
-        // The last CTA to run out of work leaves the queue ready for the next launch.
-        const uint32_t done = atomicAdd(a.queue + 1, 1u);
-        if (done == gridDim.x - 1) { a.queue[0] = 0; a.queue[1] = 0; }
         return;
     }
 
@@ -538,7 +578,8 @@ static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t 
 }
 
 int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                           float* partials, uint32_t* counters, uint32_t* queue, cudaStream_t s) {
+                           float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
+                           cudaStream_t s) {
     if (t->n_items == 0) return QVX_OK;
     const Layout& L = t->L;
     if (t->item_words > REC_WORDS)
@@ -549,6 +590,9 @@ int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, con
     StreamArgs a;
     a.pool = (const uint8_t*)pool; a.q = q; a.out = out; a.partials = partials; a.counters = counters; a.queue = queue;
     a.items = t->d_items; a.status = device_status_word(dev);
+    a.k_new = k_new; a.v_new = v_new; a.kv_out = L.kvh * L.d;
+    if (k_new && (((uintptr_t)k_new | (uintptr_t)v_new) & 15u))
+        return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: k_new and v_new must be 16-byte aligned");
     a.block_bytes = L.block_bytes; a.page_bytes = L.page_bytes; a.tiles_per_block = L.B / TILE;
     a.heads = (uint32_t)t->heads; a.item_words = t->item_words; a.n_items = (uint32_t)t->n_items;
     a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;

@@ -42,6 +42,7 @@ static uint64_t now_ns() {
 // ---- launch timing ---------------------------------------------------------------------------
 LaunchTimer::LaunchTimer(qvx_device* dev, int kind, cudaStream_t s) : dev(dev), kind(kind), s(s) {
     if (!dev || !dev->cfg.timing) return;
+    if (dev->timing_seen[kind]++ % dev->cfg.timing != 0) return;  // timing = n: every n-th launch of a kind
     auto get = [&]() {
         cudaEvent_t e = nullptr;
         if (!dev->event_pool.empty()) { e = dev->event_pool.back(); dev->event_pool.pop_back(); }
@@ -279,10 +280,15 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
         for (uint32_t grp = 0; grp < groups; grp++)
             for (uint32_t c = 0; c < nch; c++) keys.push_back(Key{std::min(chunk, len - c * chunk), (uint32_t)t, grp, c});
     }
-    std::stable_sort(keys.begin(), keys.end(), [](const Key& a, const Key& b) { return a.tokens > b.tokens; });
+    // (a counting sort: tokens <= chunk, and this runs once per op on the host's critical path)
+    std::vector<uint32_t> start(chunk + 2, 0);
+    for (const Key& k : keys) start[chunk - k.tokens + 1]++;
+    for (uint32_t v = 0; v <= chunk; v++) start[v + 1] += start[v];
+    std::vector<uint32_t> order(keys.size());
+    for (uint32_t i = 0; i < keys.size(); i++) order[start[chunk - keys[i].tokens]++] = i;
     uint32_t* items = (uint32_t*)(img + im.off_items);
     for (size_t n = 0; n < keys.size(); n++) {
-        const Key& k = keys[n];
+        const Key& k = keys[order[n]];
         uint32_t t = k.seq, len = pos[t] + 1u, nch = (len + chunk - 1) / chunk;
         uint32_t kvh = k.grp / gpk, sub = k.grp % gpk;
         uint32_t* w = items + n * im.item_words;
@@ -343,15 +349,25 @@ static int32_t ensure_partials(qvx_device* dev, size_t floats, size_t counters) 
     return QVX_OK;
 }
 
+// Attention, with the step's KV append in front of it when k_new / v_new are given: inside the
+// same launch where the kernel can (16-bit native pools), as its own launch otherwise.
 static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                             uint32_t variant, cudaStream_t s) {
+                             uint32_t variant, cudaStream_t s, const float* k_new = nullptr, const float* v_new = nullptr) {
     bool split_ok = attn_split_supported(t->L, t->heads) && t->n_items > 0;
     if (variant == QVX_ATTN_SPLIT && !attn_split_supported(t->L, t->heads))
         return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no split attention kernel for this geometry");
-    if (variant == QVX_ATTN_EXACT || !split_ok) return launch_attn_exact(dev, t, pool, q, out, s);
+    const bool split = variant != QVX_ATTN_EXACT && split_ok;
+    const bool fused = split && k_new && attn_split_fuses_append(t->L, t->heads);
+    if (k_new && !fused) {
+        int32_t rc = launch_kv_rows(dev, t->L, const_cast<void*>(pool), k_new, v_new, (size_t)t->L.kvh * t->L.d, nullptr, t->d_pos,
+                                    t->d_blocks, t->d_table_at, t->s, QVX_K_APPEND, s);
+        if (rc) return rc;
+    }
+    if (!split) return launch_attn_exact(dev, t, pool, q, out, s);
     int32_t rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
     if (rc) return rc;
-    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, dev->counters, dev->queue, s);
+    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, dev->counters, dev->queue, fused ? k_new : nullptr,
+                             fused ? v_new : nullptr, s);
 }
 
 }  // namespace qvx
@@ -648,6 +664,14 @@ int32_t qvx_attn_decode(qvx_device* dev, qvx_tables* tables, const void* pool, c
     return run_attention(dev, tables, pool, q, out, variant, (cudaStream_t)stream);
 }
 
+int32_t qvx_kv_append_attn_decode(qvx_device* dev, qvx_tables* tables, void* pool, const float* k_new, const float* v_new,
+                                  const float* q, float* out, uint32_t variant, void* stream) {
+    if (!dev || !tables || tables->dev != dev || !k_new || !v_new) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    return run_attention(dev, tables, pool, q, out, variant, (cudaStream_t)stream, k_new, v_new);
+}
+
 int32_t qvx_block_copy(qvx_device* dev, const qvx_geometry* geo, void* pool, size_t pool_blocks, const uint32_t* src,
                        const uint32_t* dst, size_t n, void* stream) {
     if (!dev) return QVX_ERR_SHAPE;
@@ -741,11 +765,9 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     const float* d_sync = (const float*)(ds + o_sync);
     rc = launch_kv_rows(dev, L, pool->ptr, d_sync, d_sync + kv_out, 2 * kv_out, (const uint32_t*)(ds + o_syncto), nullptr,
                         nullptr, nullptr, n_sync, QVX_K_SYNC, cs);
-    if (rc == QVX_OK)
-        rc = launch_kv_rows(dev, L, pool->ptr, (const float*)(ds + o_k), (const float*)(ds + o_v), kv_out, nullptr,
-                            t->d_pos, t->d_blocks, t->d_table_at, s, QVX_K_APPEND, cs);
     if (rc == QVX_OK && s)
-        rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), (float*)(ds + o_out), variant, cs);
+        rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), (float*)(ds + o_out), variant, cs,
+                           (const float*)(ds + o_k), (const float*)(ds + o_v));
     if (rc) return rc;
     cudaEvent_t ev_done = next_event(x);
     cudaEventRecord(ev_done, cs);

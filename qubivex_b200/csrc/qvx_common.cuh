@@ -141,6 +141,7 @@ struct qvx_device {
     qvx_usage usage{};
     qvx_transfer_stats xfer{};
     qvx_kernel_times ktimes{};
+    uint64_t timing_seen[QVX_K_COUNT] = {};
     std::vector<qvx::TimedLaunch> pending;  // events not read back yet
     std::vector<cudaEvent_t> event_pool;
     // Scratch the split kernel writes its partial results to, and the arrival counters of the
@@ -214,7 +215,9 @@ struct qvx_tables {
 
 namespace qvx {
 int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                          float* partials, uint32_t* counters, uint32_t* queue, cudaStream_t s);
+                          float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
+                          cudaStream_t s);
+bool attn_split_fuses_append(const Layout& L, size_t heads);
 int32_t launch_attn_exact(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                           cudaStream_t s);
 size_t attn_partial_floats(const qvx_tables* t);  // floats of scratch the split kernel needs

@@ -102,10 +102,10 @@ class DeviceBuffer:
 class CudaDevice:
     """`impl DiscreteDevice for CudaDevice`, the decode-attention subset."""
 
-    def __init__(self, device: int = 0, capacity: int = 0, kv_pool: int = 0, timing: bool = False):
+    def __init__(self, device: int = 0, capacity: int = 0, kv_pool: int = 0, timing: int | bool = False):
         self.lib = _lib.load()
         self.h = C.c_void_p()
-        cfg = Config(device, capacity, kv_pool, 1 if timing else 0)
+        cfg = Config(device, capacity, kv_pool, int(timing))  # timing = n: CUDA events around every n-th launch
         rc = self.lib.qvx_open(C.byref(cfg), C.byref(self.h))
         if rc:
             raise _ERRORS.get(rc, ComputeError)(self.lib.qvx_last_error(None).decode())

@@ -240,7 +240,11 @@ def test_kernel_times_are_counted(dev):
     c = Case(32, 4, 128, 16, "bf16", [600, 100], seed=81)
     c.run_device(dev, variant=qd.ATTN_SPLIT)
     kt = dev.kernel_times()
-    assert kt["sync"][0] == 1 and kt["append"][0] == 1 and kt["attn"][0] == 1
+    c32 = Case(8, 2, 64, 16, "f32", [600, 100], seed=82)
+    c32.run_device(dev, variant=qd.ATTN_SPLIT)
+    assert dev.kernel_times()["append"][0] == 1   # f32 pool: its own launch
+    assert kt["sync"][0] == 1 and kt["attn"][0] == 1
+    assert kt["append"][0] == 0   # 16-bit native pool: the append rides in the attention launch
     assert kt["attn"][1] > 0
     t = dev.transfers()
-    assert t.submissions >= 1 and t.activations_out >= c.q.nbytes and t.timed >= 3
+    assert t.submissions >= 1 and t.activations_out >= c.q.nbytes and t.timed >= 2
