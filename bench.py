@@ -224,11 +224,16 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     out = torch.empty((s, heads, d), device="cuda")
     pool_p, sp = C.c_void_p(pool.ptr), C.c_void_p(stream)
 
+    # Consecutive launches serve different layers, whose blocks are disjoint: the next layer's old
+    # positions may start streaming while this layer's launch drains (its q, k_new and v_new still
+    # wait for everything before it in the stream).
+    variant = qd.ATTN_AUTO | (qd.ATTN_POOL_SETTLED if layers >= 2 else 0)
+
     def step(t: int):
         for l in range(layers):
             tb = tabs[t][l]
             # the step's append and its attention: one launch (the rows are stored by the CTAs that read them)
-            dev.check(lib.qvx_kv_append_attn_decode(dev.h, tb, pool_p, ptr(kn[t]), ptr(vn[t]), ptr(q[t]), ptr(out), qd.ATTN_AUTO, sp))
+            dev.check(lib.qvx_kv_append_attn_decode(dev.h, tb, pool_p, ptr(kn[t]), ptr(vn[t]), ptr(q[t]), ptr(out), variant, sp))
 
     def barrier():
         torch.cuda.synchronize()

@@ -162,6 +162,13 @@ const uint32_t *qvx_tables_table_at(qvx_tables *t);
 #define QVX_ATTN_AUTO 0   /* the split kernel */
 #define QVX_ATTN_SPLIT 1  /* GQA-grouped, online softmax, split over the context: within tolerance */
 #define QVX_ATTN_EXACT 2  /* the order of math::attend, bit for bit (math.rs:142-155) */
+/* May be or-ed into `variant` of the device-memory calls: the caller's word that nothing still
+ * running in the stream writes the pool blocks or the tables this launch reads (e.g. the launch
+ * before it served another layer, whose blocks are others).  Only q, k_new and v_new are then
+ * taken to come from the stream's earlier work: the launch is made a programmatic dependent
+ * launch, starts streaming the old positions while the launch before it drains, and waits
+ * (griddepcontrol.wait) before it reads q, k_new or v_new or writes anything. */
+#define QVX_ATTN_POOL_SETTLED 0x100
 
 /* Paged decode attention: `attn_decode.comp` (shaders/attn_decode.comp:60-175), the gather
  * and `attend` of sim.rs:400-429.  q, out: s x heads x head_dim f32, [token][head][d].

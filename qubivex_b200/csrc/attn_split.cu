@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
 bool attn_stream_supported(const Layout& L, size_t heads);
 int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                            float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
-                           cudaStream_t s);
+                           bool overlap, cudaStream_t s);
 
 bool attn_split_supported(const Layout& L, size_t heads) {
     if (L.layout != QVX_LAYOUT_NATIVE) return false;
@@ -378,10 +378,10 @@ bool attn_split_fuses_append(const Layout& L, size_t heads) { return attn_stream
 
 int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                           float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
-                          cudaStream_t s) {
+                          bool overlap, cudaStream_t s) {
     if (t->n_items == 0) return QVX_OK;
     const Layout& L = t->L;
-    if (L.dtype != QVX_F32) return launch_attn_stream(dev, t, pool, q, out, partials, counters, queue, k_new, v_new, s);
+    if (L.dtype != QVX_F32) return launch_attn_stream(dev, t, pool, q, out, partials, counters, queue, k_new, v_new, overlap, s);
     SplitArgs a;
     a.pool = (const uint8_t*)pool; a.q = q; a.out = out; a.partials = partials; a.counters = counters;
     a.items = t->d_items; a.status = device_status_word(dev);

@@ -65,8 +65,15 @@ struct StreamArgs {
     const float* v_new;
     uint64_t block_bytes;
     uint32_t page_bytes, tiles_per_block, heads, item_words, n_items, kv_out;
+    uint32_t overlap;       // the pool and the tables do not depend on the work before this launch in the stream
     float scale_log2;
 };
+
+// Programmatic dependent launch: `grid_dep_wait` returns once everything earlier in the stream
+// has completed and is visible (at once when the launch did not ask for the overlap);
+// `grid_dep_launch` lets the next launch in the stream start filling SMs this grid has left.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -125,11 +132,28 @@ __device__ __forceinline__ void deliver(const StreamArgs& a, const Mail& it, uin
     const float* ml = p0 + 8 * D;
     const uint32_t hl = lane & 7;
     float M = -INFINITY, L = 0.f;
-    for (uint32_t c = lane >> 3; c < it.nch; c += 4) M = fmaxf(M, __ldcg(ml + (size_t)c * PART_STRIDE + hl));
-    M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
-    M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
-    for (uint32_t c = lane >> 3; c < it.nch; c += 4)
-        L = fmaf(__ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl), ex2(__ldcg(ml + (size_t)c * PART_STRIDE + hl) - M), L);
+    if (it.nch <= 32) {
+        // One round of loads for the maxima and the row sums of up to 32 chunks.
+        float mv[8], lv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const uint32_t c = (lane >> 3) + 4 * u;
+            mv[u] = c < it.nch ? __ldcg(ml + (size_t)c * PART_STRIDE + hl) : -INFINITY;
+            lv[u] = c < it.nch ? __ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) M = fmaxf(M, mv[u]);
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+#pragma unroll
+        for (int u = 0; u < 8; u++) L = fmaf(lv[u], ex2(mv[u] - M), L);
+    } else {
+        for (uint32_t c = lane >> 3; c < it.nch; c += 4) M = fmaxf(M, __ldcg(ml + (size_t)c * PART_STRIDE + hl));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
+        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+        for (uint32_t c = lane >> 3; c < it.nch; c += 4)
+            L = fmaf(__ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl), ex2(__ldcg(ml + (size_t)c * PART_STRIDE + hl) - M), L);
+    }
     L += __shfl_xor_sync(0xffffffffu, L, 8);
     L += __shfl_xor_sync(0xffffffffu, L, 16);
     // Lane x owns float4 column x of every head when D = 128; in general output i = lane + 32 j.
@@ -192,6 +216,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + SM::abort_off);
     volatile Mail* mailbox = reinterpret_cast<volatile Mail*>(smem + SM::mail_off);
 
+    if (threadIdx.x == 0) grid_dep_launch();
+    // Without the caller's word that the pool is settled, nothing is touched before the stream's
+    // earlier work is done.  With it, only what that work produces (q, k_new, v_new) and what
+    // this grid writes wait for it; the old positions' tiles start streaming right away.
+    if (!a.overlap) grid_dep_wait();
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < SM::stages; s++) { mbar_init(full0 + s * 8, 1); mbar_init(empty0 + s * 8, 1); }
         for (uint32_t s = 0; s < Q_SLOTS; s++) { mbar_init(qfull0 + s * 8, 1); mbar_init(qempty0 + s * 8, CW); }
@@ -244,12 +273,39 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 break;
             }
             const uint8_t* base = a.pool + (uint64_t)kvh * 2u * a.page_bytes;
+            const uint32_t ntiles = (tokens + TILE - 1) / TILE;
+            auto issue_tile = [&](uint32_t tau) -> bool {  // lane 0 only
+                const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
+                if (!mbar_wait(empty0 + st * 8, ph ^ 1)) return false;
+                const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + tau / a.tiles_per_block];
+                const uint8_t* src = base + (uint64_t)blk * a.block_bytes + (uint64_t)(tau % a.tiles_per_block) * SM::tile_bytes;
+                const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
+                mbar_expect_tx(full0 + st * 8, SM::stage_bytes);
+                if (a.page_bytes == SM::tile_bytes) {  // one tile per block: its values follow its keys
+                    bulk_g2s(dst, src, SM::stage_bytes, full0 + st * 8);
+                } else {
+                    bulk_g2s(dst, src, SM::tile_bytes, full0 + st * 8);
+                    bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, full0 + st * 8);
+                }
+                n++;
+                return true;
+            };
+            const bool last_chunk = rec[4] == NO_PART || rec[4] - rec[5] == rec[6] - 1;
+            uint32_t tau0 = 0;
+            if (k == 0 && a.overlap) {
+                // The first item's old positions stream while the stream's earlier work finishes;
+                // a chunk that holds the step's new row waits, since its rows come from that work.
+                if (lane == 0 && !(last_chunk && a.k_new != nullptr)) {
+                    const uint32_t pre = ntiles < SM::stages ? ntiles : SM::stages;
+                    for (; tau0 < pre; tau0++)
+                        if (!issue_tile(tau0)) { failed = true; break; }
+                }
+                grid_dep_wait();
+            }
             if (a.k_new != nullptr) {
                 // KV append fused in: the chunk that ends the sequence holds the position the step
                 // adds.  Its rows go into the pool now, long before the tile that reads them is
                 // asked for (sim.rs:394-398: the new row is stored, then attention reads 0..=pos).
-                const uint32_t part = rec[4], part0 = rec[5], nch = rec[6];
-                const bool last_chunk = part == NO_PART || part - part0 == nch - 1;
                 if (last_chunk) {
                     const uint32_t p = tokens - 1, B = a.tiles_per_block * TILE, slot = p % B;
                     const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + p / B];
@@ -283,21 +339,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     queue_dry = idx_next >= a.n_items;
                     if (!queue_dry) idx_next = gridDim.x + atomicAdd(a.queue, 1u);
                 }
-                const uint32_t ntiles = (tokens + TILE - 1) / TILE;
-                for (uint32_t tau = 0; tau < ntiles; tau++, n++) {
-                    const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
-                    if (!mbar_wait(empty0 + st * 8, ph ^ 1)) { failed = true; break; }
-                    const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + tau / a.tiles_per_block];
-                    const uint8_t* src = base + (uint64_t)blk * a.block_bytes + (uint64_t)(tau % a.tiles_per_block) * SM::tile_bytes;
-                    const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
-                    mbar_expect_tx(full0 + st * 8, SM::stage_bytes);
-                    if (a.page_bytes == SM::tile_bytes) {  // one tile per block: its values follow its keys
-                        bulk_g2s(dst, src, SM::stage_bytes, full0 + st * 8);
-                    } else {
-                        bulk_g2s(dst, src, SM::tile_bytes, full0 + st * 8);
-                        bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, full0 + st * 8);
-                    }
-                }
+                for (uint32_t tau = tau0; tau < ntiles && !failed; tau++)
+                    if (!issue_tile(tau)) failed = true;
             }
             if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
         }
@@ -318,6 +361,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         // Takes the chunks whose partials the consumers have stored, one mail each, and does
         // what would otherwise stall them: the device-wide fence, the arrival count and, for
         // the last chunk of a sequence to arrive, the merge.
+        if (a.overlap) grid_dep_wait();
         for (uint32_t kp = 0;; kp++) {
             const uint32_t ms = kp % MAIL_SLOTS;
             if (!__all_sync(0xffffffffu, mbar_wait(mfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;  // the abort path
@@ -463,6 +507,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             *abort_flag = 1;
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
         }
+        if (k == 0 && a.overlap) grid_dep_wait();  // before this grid's first write to `out` or the scratch
         // ---- the consumers' states meet in shared memory --------------------------------------
         consumer_barrier();  // the previous item's merge has read everything it needed
         if (*abort_flag) return;  // uniform: every consumer warp sees the flag after the barrier
@@ -573,13 +618,18 @@ static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t 
         if (ctas_per_sm < 1) ctas_per_sm = 1;
     }
     const unsigned grid = (unsigned)std::min<size_t>(a.n_items, (size_t)ctas_per_sm * dev->prop.multiProcessorCount);
-    kernel<<<grid, STREAM_THREADS, StreamSmem<D>::total, s>>>(a);
-    return check_cuda(dev, cudaGetLastError(), "streaming attention launch");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(STREAM_THREADS); cfg.dynamicSmemBytes = StreamSmem<D>::total; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = a.overlap ? 1 : 0;
+    return check_cuda(dev, cudaLaunchKernelEx(&cfg, kernel, a), "streaming attention launch");
 }
 
 int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                            float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
-                           cudaStream_t s) {
+                           bool overlap, cudaStream_t s) {
     if (t->n_items == 0) return QVX_OK;
     const Layout& L = t->L;
     if (t->item_words > REC_WORDS)
@@ -590,7 +640,7 @@ int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, con
     StreamArgs a;
     a.pool = (const uint8_t*)pool; a.q = q; a.out = out; a.partials = partials; a.counters = counters; a.queue = queue;
     a.items = t->d_items; a.status = device_status_word(dev);
-    a.k_new = k_new; a.v_new = v_new; a.kv_out = L.kvh * L.d;
+    a.k_new = k_new; a.v_new = v_new; a.kv_out = L.kvh * L.d; a.overlap = overlap ? 1u : 0u;
     if (k_new && (((uintptr_t)k_new | (uintptr_t)v_new) & 15u))
         return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: k_new and v_new must be 16-byte aligned");
     a.block_bytes = L.block_bytes; a.page_bytes = L.page_bytes; a.tiles_per_block = L.B / TILE;

@@ -101,8 +101,8 @@ static int32_t check_status(qvx_device* dev) {
     *(volatile int*)x->status_host = 0;
     if (dev->counters) {  // an item that gave up never arrived: start the counters from zero again
         cudaDeviceSynchronize();
-        cudaMemset(dev->counters, 0, dev->counters_cap * 4);
-        if (dev->queue) cudaMemset(dev->queue, 0, 8);
+        cudaMemset(dev->counters, 0, 2 * dev->counters_cap * 4);
+        if (dev->queue) cudaMemset(dev->queue, 0, 16);
     }
     return fail(dev, QVX_ERR_DEVICE, "cuda device error: %s (status %d); the op's outputs are not valid",
                 st == 2 ? "a position beyond the bound the caller gave" : "a kernel gave up a bounded wait", st);
@@ -327,22 +327,22 @@ static int32_t ensure_partials(qvx_device* dev, size_t floats, size_t counters) 
     if (floats * 4 > dev->partials_cap) {
         if (dev->partials) cudaFree(dev->partials);
         dev->partials = nullptr; dev->partials_cap = 0;
-        size_t cap = std::max<size_t>(floats * 4 * 5 / 4, 1u << 20);
-        e = cudaMalloc(&dev->partials, cap);
+        size_t cap = (std::max<size_t>(floats * 4 * 5 / 4, 1u << 20) + 255) & ~(size_t)255;
+        e = cudaMalloc(&dev->partials, 2 * cap);  // two halves, used by alternate launches
         if (e != cudaSuccess) return check_cuda(dev, e, "partials");
         dev->partials_cap = cap;
     }
     if (!dev->queue) {
-        e = cudaMalloc((void**)&dev->queue, 8);
-        if (e == cudaSuccess) e = cudaMemset(dev->queue, 0, 8);
+        e = cudaMalloc((void**)&dev->queue, 16);
+        if (e == cudaSuccess) e = cudaMemset(dev->queue, 0, 16);
         if (e != cudaSuccess) return check_cuda(dev, e, "work queue");
     }
     if (counters > dev->counters_cap) {
         if (dev->counters) cudaFree(dev->counters);
         dev->counters = nullptr; dev->counters_cap = 0;
         size_t cap = std::max<size_t>(counters * 2, 4096);
-        e = cudaMalloc((void**)&dev->counters, cap * 4);
-        if (e == cudaSuccess) e = cudaMemset(dev->counters, 0, cap * 4);  // every launch leaves them at zero again
+        e = cudaMalloc((void**)&dev->counters, 2 * cap * 4);
+        if (e == cudaSuccess) e = cudaMemset(dev->counters, 0, 2 * cap * 4);  // every launch leaves them at zero again
         if (e != cudaSuccess) return check_cuda(dev, e, "arrival counters");
         dev->counters_cap = cap;
     }
@@ -352,7 +352,8 @@ static int32_t ensure_partials(qvx_device* dev, size_t floats, size_t counters) 
 // Attention, with the step's KV append in front of it when k_new / v_new are given: inside the
 // same launch where the kernel can (16-bit native pools), as its own launch otherwise.
 static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                             uint32_t variant, cudaStream_t s, const float* k_new = nullptr, const float* v_new = nullptr) {
+                             uint32_t variant_flags, cudaStream_t s, const float* k_new = nullptr, const float* v_new = nullptr) {
+    const uint32_t variant = variant_flags & 0xffu;
     bool split_ok = attn_split_supported(t->L, t->heads) && t->n_items > 0;
     if (variant == QVX_ATTN_SPLIT && !attn_split_supported(t->L, t->heads))
         return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no split attention kernel for this geometry");
@@ -366,8 +367,12 @@ static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, c
     if (!split) return launch_attn_exact(dev, t, pool, q, out, s);
     int32_t rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
     if (rc) return rc;
-    return launch_attn_split(dev, t, pool, q, out, (float*)dev->partials, dev->counters, dev->queue, fused ? k_new : nullptr,
-                             fused ? v_new : nullptr, s);
+    const uint32_t half = dev->scratch_half;
+    dev->scratch_half ^= 1u;
+    const bool overlap = (variant_flags & QVX_ATTN_POOL_SETTLED) != 0;
+    return launch_attn_split(dev, t, pool, q, out, (float*)((char*)dev->partials + half * dev->partials_cap),
+                             dev->counters + half * dev->counters_cap, dev->queue + 2 * half, fused ? k_new : nullptr,
+                             fused ? v_new : nullptr, overlap, s);
 }
 
 }  // namespace qvx
@@ -700,12 +705,13 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     for (size_t i = 0; i < n_sync; i++)
         if (sync_to[i] / L.B >= held)
             return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: a block past the pool's %zu", held);
-    if (variant == QVX_ATTN_SPLIT && !attn_split_supported(L, heads))
+    if ((variant & 0xffu) == QVX_ATTN_SPLIT && !attn_split_supported(L, heads))
         return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no split attention kernel for this geometry");
     if (s == 0 && n_sync == 0) return QVX_OK;
 
     const size_t kv_out = (size_t)L.kvh * L.d, q_out = heads * L.d;
-    const bool split = attn_split_supported(L, heads) && variant != QVX_ATTN_EXACT;
+    const bool split = attn_split_supported(L, heads) && (variant & 0xffu) != QVX_ATTN_EXACT;
+    variant &= 0xffu;  // the host op orders its own copies and kernels: no overlap with what precedes it
     TableImage im = plan_image(L, heads, s, pos, n_blocks, split);
     if (im.max_nch > MAX_CHUNKS) return too_many_chunks(dev, im.max_nch);
     // Staged on the device for this op: the tables image, sync_to, q, k_new, v_new, sync rows, out.

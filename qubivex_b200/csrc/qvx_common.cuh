@@ -151,6 +151,9 @@ struct qvx_device {
     uint32_t* counters = nullptr;
     size_t counters_cap = 0;
     uint32_t* queue = nullptr;  // the streaming kernel's work queue: next item, CTAs done
+    // The scratch comes twice: consecutive launches alternate halves, so that a launch allowed to
+    // overlap the tail of the one before never shares partials, counters or queue with it.
+    uint32_t scratch_half = 0;
     // Pinned staging for the _host calls, grown on demand; `staging_used` is reset by qvx_wait.
     char* staging = nullptr;
     size_t staging_cap = 0, staging_used = 0;
@@ -216,7 +219,7 @@ struct qvx_tables {
 namespace qvx {
 int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                           float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
-                          cudaStream_t s);
+                          bool overlap, cudaStream_t s);
 bool attn_split_fuses_append(const Layout& L, size_t heads);
 int32_t launch_attn_exact(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                           cudaStream_t s);

@@ -18,6 +18,7 @@ from ._lib import Config, Geometry, KernelTimes, TransferStats, Usage
 F32, BF16, F16 = 0, 1, 2
 LAYOUT_REFERENCE, LAYOUT_NATIVE = 0, 1
 ATTN_AUTO, ATTN_SPLIT, ATTN_EXACT = 0, 1, 2
+ATTN_POOL_SETTLED = 0x100  # or-ed into a variant: see QVX_ATTN_POOL_SETTLED in include/qvx.h
 KV_BLOCK = 256  # crates/qubivex-compute/src/discrete.rs:248
 
 

@@ -248,3 +248,60 @@ def test_kernel_times_are_counted(dev):
     assert kt["attn"][1] > 0
     t = dev.transfers()
     assert t.submissions >= 1 and t.activations_out >= c.q.nbytes and t.timed >= 2
+
+
+def test_layers_back_to_back_with_the_pool_settled_flag_give_the_same_bits(dev):
+    """Several layers' launches queued back to back, each told that its pool blocks are settled
+    (so it may start under the tail of the launch before it), against the same launches one at
+    a time: outputs and pool bytes must be identical."""
+    torch = pytest.importorskip("torch")
+    import ctypes as C
+    from qubivex_b200.device import ptr
+    heads, kvh, d, B, s, layers, steps = 32, 4, 128, 16, 12, 4, 3
+    geo = qd.geometry(B, kvh, d, qd.BF16)
+    bb = qd.block_bytes(geo)
+    rng = np.random.default_rng(91)
+    lengths = rng.integers(500, 1500, size=s)
+    nb = (lengths + steps + B - 1) // B
+    per_layer = int(nb.sum())
+    perm = rng.permutation(per_layer * layers).astype(np.uint32)
+    table_at = np.concatenate([[0], np.cumsum(nb)[:-1]]).astype(np.uint32)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    pool0 = torch.randn(per_layer * layers * bb // 2, device="cuda", generator=g).to(torch.bfloat16)
+    q = [torch.randn((s, heads, d), device="cuda", generator=g) for _ in range(steps)]
+    kn = [torch.randn((s, kvh * d), device="cuda", generator=g) for _ in range(steps)]
+    vn = [torch.randn((s, kvh * d), device="cuda", generator=g) for _ in range(steps)]
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def run(flag, sync_each):
+        pool = pool0.clone()
+        outs = []
+        tabs = []
+        for t in range(steps):
+            pos = (lengths + t).astype(np.uint32)
+            for l in range(layers):
+                tb = C.c_void_p()
+                blocks = perm[l * per_layer:(l + 1) * per_layer].copy()
+                dev.check(dev.lib.qvx_tables_create(dev.h, C.byref(geo), per_layer * layers, heads, s, ptr(pos), ptr(blocks), per_layer,
+                                                    ptr(table_at), C.byref(tb)))
+                tabs.append(tb)
+        i = 0
+        for t in range(steps):
+            for l in range(layers):
+                out = torch.empty((s, heads, d), device="cuda")
+                dev.check(dev.lib.qvx_kv_append_attn_decode(dev.h, tabs[i], ptr(pool), ptr(kn[t]), ptr(vn[t]), ptr(q[t]), ptr(out),
+                                                            qd.ATTN_SPLIT | flag, stream))
+                if sync_each:
+                    torch.cuda.synchronize()
+                outs.append(out)
+                i += 1
+        torch.cuda.synchronize()
+        dev.kernel_times()
+        for tb in tabs:
+            dev.lib.qvx_tables_free(tb)
+        return torch.stack(outs).cpu().numpy(), pool.cpu().view(torch.int16).numpy()
+
+    want_out, want_pool = run(0, True)
+    got_out, got_pool = run(qd.ATTN_POOL_SETTLED, False)
+    assert np.array_equal(got_pool, want_pool)
+    assert np.array_equal(got_out.view(np.uint32), want_out.view(np.uint32))
