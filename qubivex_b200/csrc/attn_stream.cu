@@ -37,6 +37,10 @@
 // bf16 carries 8 mantissa bits: queries and probabilities go through the tensor cores as a
 // 16-bit value plus a 16-bit remainder (two passes), which keeps the result within 1e-5 of the
 // f32 arithmetic instead of 5e-3.  f16's 11 bits need one pass.
+#include <stdio.h>
+
+#include <vector>
+
 #include "attn_ptx.cuh"
 
 namespace qvx {
@@ -74,6 +78,16 @@ struct StreamArgs {
 // `grid_dep_launch` lets the next launch in the stream start filling SMs this grid has left.
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifdef QVX_TRACE
+// Experiment builds only: per-CTA timestamps of the kernel's phases, dumped by the host.
+constexpr int TRACE_PER_CTA = 256;
+__device__ unsigned long long g_trace[512 * TRACE_PER_CTA];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define TRACE(slot_var, tag) do { if ((slot_var) < TRACE_PER_CTA / 4) { g_trace[blockIdx.x * TRACE_PER_CTA + trace_base + (slot_var)] = (gtime() << 8) | (tag); (slot_var)++; } } while (0)
+#else
+#define TRACE(slot_var, tag) do { } while (0)
+#endif
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -252,6 +266,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         };
         uint32_t n = 0;          // tiles issued so far, over all items
         bool failed = false, queue_dry = false;
+#ifdef QVX_TRACE
+        const uint32_t trace_base = 0; uint32_t tp = 0;
+        if (lane == 0) TRACE(tp, 1);   // producer start
+#endif
         uint32_t idx_next = 0;
         if (lane == 0) {
             // The first item needs no atomic: CTA b starts with item b, the queue hands out the rest.
@@ -339,8 +357,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     queue_dry = idx_next >= a.n_items;
                     if (!queue_dry) idx_next = gridDim.x + atomicAdd(a.queue, 1u);
                 }
+#ifdef QVX_TRACE
+                TRACE(tp, 2);  // item issue begins
+#endif
                 for (uint32_t tau = tau0; tau < ntiles && !failed; tau++)
                     if (!issue_tile(tau)) failed = true;
+#ifdef QVX_TRACE
+                TRACE(tp, 3);  // item issue ends
+#endif
             }
             if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
         }
@@ -349,6 +373,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 *abort_flag = 1;
                 atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             }
+#ifdef QVX_TRACE
+            TRACE(tp, 4);  // producer exit
+#endif
             // The last CTA to run out of work leaves the queue ready for the next launch.
             const uint32_t done = atomicAdd(a.queue + 1, 1u);
             if (done == gridDim.x - 1) { a.queue[0] = 0; a.queue[1] = 0; }
@@ -362,6 +389,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         // what would otherwise stall them: the device-wide fence, the arrival count and, for
         // the last chunk of a sequence to arrive, the merge.
         if (a.overlap) grid_dep_wait();
+#ifdef QVX_TRACE
+        const uint32_t trace_base = TRACE_PER_CTA / 4; uint32_t tp = 0;
+#endif
         for (uint32_t kp = 0;; kp++) {
             const uint32_t ms = kp % MAIL_SLOTS;
             if (!__all_sync(0xffffffffu, mbar_wait(mfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;  // the abort path
@@ -370,8 +400,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             m.nch = mailbox[ms].nch; m.counter = mailbox[ms].counter; m.stop = mailbox[ms].stop;
             __syncwarp();
             if (lane == 0) mbar_arrive(mfree0 + ms * 8);
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, m.stop ? 12 : 10);  // mail taken / stop
+#endif
             if (m.stop) return;
             deliver<D>(a, m, lane);
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, 11);  // deliver done
+#endif
         }
     }
 
@@ -387,6 +423,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     float* res = res_all + warp * SM::res_floats;
     uint32_t nbase = 0;   // tiles of the items before this one
     uint32_t kp = 0;      // mails sent to the epilogue warp so far
+#ifdef QVX_TRACE
+    const uint32_t trace_base = TRACE_PER_CTA / 2 + (warp == 0 ? 0 : TRACE_PER_CTA / 4); uint32_t tp = 0;
+    const bool tr = lane == 0 && (warp == 0 || warp == CW - 1);
+#endif
     bool dead = false;    // this warp gave up a wait: it only keeps the barriers company from here on
     for (uint32_t k = 0;; k++) {
         const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
@@ -400,6 +440,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             it.part = rec[4]; it.part0 = rec[5]; it.nch = rec[6]; it.counter = rec[7];
             if (it.tokens == 0) break;  // the end of the queue: every consumer warp reads the same record
         }
+#ifdef QVX_TRACE
+        if (tr) TRACE(tp, 20);  // item header read
+#endif
         // The warp that takes the item's tiles 0, CW, 2 CW, ...: the merge below goes through the
         // warps in the order of the tiles they took, so that the sum order does not depend on
         // how many tiles this CTA happened to stream before the item.
@@ -497,6 +540,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
             nbase += ntiles;
         }
+#ifdef QVX_TRACE
+        if (tr) TRACE(tp, 21);  // tiles done
+#endif
         // Row sums over the positions held by the other lanes of the same t.
 #pragma unroll
         for (int sh = 4; sh <= 16; sh <<= 1) {
@@ -523,6 +569,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             res[16 + (2 * t + 1) * D + 16 * mt + g + 8] = o[mt][3];
         }
         consumer_barrier();
+#ifdef QVX_TRACE
+        if (tr) TRACE(tp, 22);  // both barriers passed
+#endif
         // Each thread merges its share of the item's float4 outputs over the CW warps.
         const bool direct = it.part == NO_PART;
         float* pbase = direct ? nullptr : a.partials + (size_t)it.part * PART_STRIDE;
@@ -580,6 +629,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         __syncwarp();
         if (lane == 0) mbar_arrive(mfull0 + ms * 8);
         kp++;
+#ifdef QVX_TRACE
+        if (tr) TRACE(tp, 23);  // mail sent
+#endif
     }
     // The end of the queue: tell the epilogue warp to finish what it holds and leave.
     {
@@ -624,6 +676,22 @@ static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = a.overlap ? 1 : 0;
+#ifdef QVX_TRACE
+    {
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
+        const char* path = getenv("QVX_TRACE_FILE");
+        if (e == cudaSuccess && path) {
+            cudaDeviceSynchronize();
+            std::vector<unsigned long long> h(512 * TRACE_PER_CTA);
+            cudaMemcpyFromSymbol(h.data(), g_trace, h.size() * 8);
+            FILE* f = fopen(path, "wb");
+            if (f) { unsigned g2 = grid; fwrite(&g2, 4, 1, f); fwrite(h.data(), 8, h.size(), f); fclose(f); }
+            cudaMemset(nullptr, 0, 0);
+            void* sym = nullptr; cudaGetSymbolAddress(&sym, g_trace); cudaMemset(sym, 0, h.size() * 8);
+        }
+        return check_cuda(dev, e, "streaming attention launch");
+    }
+#endif
     return check_cuda(dev, cudaLaunchKernelEx(&cfg, kernel, a), "streaming attention launch");
 }
 
