@@ -349,15 +349,17 @@ bool attn_split_supported(const Layout& L, size_t heads) {
 }
 
 size_t attn_stream_partial_floats(uint32_t d);
-uint32_t attn_stream_counters_per_group();
+uint32_t attn_stream_parts(uint32_t nch);
+uint32_t attn_stream_counters(uint32_t nch);
 
 // Floats of scratch for the partial results (the 16-bit kernel keeps m and l once per warp).
 size_t attn_partial_floats(const qvx_tables* t) {
     size_t one = t->L.dtype == QVX_F32 ? 8 * (size_t)t->L.d + 16 : attn_stream_partial_floats(t->L.d);
     return t->n_parts * one;
 }
-// Arrival counters per split (sequence, group).
-uint32_t attn_counters_per_group(const Layout& L) { return L.dtype == QVX_F32 ? 1u : attn_stream_counters_per_group(); }
+// Partial slots and arrival counters of one split (sequence, group) of `nch` chunks.
+uint32_t attn_parts_per_group(const Layout& L, uint32_t nch) { return L.dtype == QVX_F32 ? nch : attn_stream_parts(nch); }
+uint32_t attn_counters_per_group(const Layout& L, uint32_t nch) { return L.dtype == QVX_F32 ? 1u : attn_stream_counters(nch); }
 
 template <typename K>
 static int32_t launch_one(qvx_device* dev, K kernel, const SplitArgs& a, unsigned grid, uint32_t smem,

@@ -127,95 +127,133 @@ struct StreamSmem {
 
 // What the consumers tell the epilogue warp about a chunk whose partial they have stored.
 struct Mail {
-    uint32_t seq, head0, nheads, part0, nch, counter, stop, pad;
+    uint32_t seq, head0, nheads, part0, nch, counter, stop, chunk;
 };
 
-// Run by the epilogue warp: counts the arrival of one chunk's partial and, if it was the last
-// of its (sequence, group) to arrive, merges the partials over the chunks in chunk order.
+// The partial results of a split sequence are merged as a tree of fan-in MERGE_FAN: entry i of
+// level k belongs to node i / MERGE_FAN; the warp that delivers the last entry of a node merges
+// the node's entries (in entry order) into one entry of level k + 1, or into the output when the
+// level has at most MERGE_FAN entries.  The tree is a function of the chunk count alone, so the
+// sum order is fixed; no merge reads more than MERGE_FAN entries, so the work left after a
+// sequence's last chunk does not grow with its length.
+#ifndef QVX_MERGE_FAN
+#define QVX_MERGE_FAN 8
+#endif
+constexpr uint32_t MERGE_FAN = QVX_MERGE_FAN;
+
+// Entries and counters one (sequence, group) of `nch` chunks needs, over all levels.
+__host__ __device__ inline uint32_t merge_entries_total(uint32_t nch) {
+    uint32_t total = nch, n = nch;
+    while (n > MERGE_FAN) { n = (n + MERGE_FAN - 1) / MERGE_FAN; total += n; }
+    return total;
+}
+__host__ __device__ inline uint32_t merge_counters_total(uint32_t nch) {
+    uint32_t total = 0, n = nch;
+    for (;;) {
+        total += (n + MERGE_FAN - 1) / MERGE_FAN;
+        if (n <= MERGE_FAN) break;
+        n = (n + MERGE_FAN - 1) / MERGE_FAN;
+    }
+    return total;
+}
+
+// Run by the epilogue warp for one chunk whose partial the consumers have stored: counts the
+// arrival and climbs the tree as far as this arrival completes nodes.
 template <int D>
-__device__ __forceinline__ void deliver(const StreamArgs& a, const Mail& it, uint32_t lane) {
+__device__ __forceinline__ void deliver(const StreamArgs& a, const Mail& it, uint32_t chunk, uint32_t lane) {
     constexpr uint32_t F4 = 8 * D / 4;
     constexpr uint32_t PART_STRIDE = 8 * D + 16;
-    __threadfence();  // the consumers' stores (seen through the mailbox barrier) are visible device-wide first
-    __syncwarp();
-    uint32_t last = 0;
-    if (lane == 0) last = atomicAdd(a.counters + it.counter, 1u) == it.nch - 1 ? 1u : 0u;
-    if (!__shfl_sync(0xffffffffu, last, 0)) return;
-    __threadfence();
-    const float* p0 = a.partials + (size_t)it.part0 * PART_STRIDE;
-    const float* ml = p0 + 8 * D;
-    const uint32_t hl = lane & 7;
-    float M = -INFINITY, L = 0.f;
-    if (it.nch <= 32) {
-        // One round of loads for the maxima and the row sums of up to 32 chunks.
-        float mv[8], lv[8];
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const uint32_t c = (lane >> 3) + 4 * u;
-            mv[u] = c < it.nch ? __ldcg(ml + (size_t)c * PART_STRIDE + hl) : -INFINITY;
-            lv[u] = c < it.nch ? __ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl) : 0.f;
-        }
-#pragma unroll
-        for (int u = 0; u < 8; u++) M = fmaxf(M, mv[u]);
-        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
-        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
-#pragma unroll
-        for (int u = 0; u < 8; u++) L = fmaf(lv[u], ex2(mv[u] - M), L);
-    } else {
-        for (uint32_t c = lane >> 3; c < it.nch; c += 4) M = fmaxf(M, __ldcg(ml + (size_t)c * PART_STRIDE + hl));
-        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
-        M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
-        for (uint32_t c = lane >> 3; c < it.nch; c += 4)
-            L = fmaf(__ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl), ex2(__ldcg(ml + (size_t)c * PART_STRIDE + hl) - M), L);
-    }
-    L += __shfl_xor_sync(0xffffffffu, L, 8);
-    L += __shfl_xor_sync(0xffffffffu, L, 16);
-    // Lane x owns float4 column x of every head when D = 128; in general output i = lane + 32 j.
-    // All of a lane's outputs advance together, two chunks at a time, so that 2 * NJ 16-byte
-    // loads are in flight per lane: the merge is a chain of L2 round trips and nothing else.
     constexpr int NJ = F4 / 32;
-    float4 acc[NJ];
-    float Mh[NJ], Lh[NJ];
-    uint32_t off[NJ];
+    const uint32_t hl = lane & 7;
+    uint32_t n = it.nch, idx = chunk, part_base = it.part0, cnt_base = it.counter;
+    for (;;) {
+        const uint32_t node = idx / MERGE_FAN, first = node * MERGE_FAN, size = min(MERGE_FAN, n - first);
+        __threadfence();  // what this entry holds (seen through the mailbox barrier, or written just above) is visible first
+        __syncwarp();
+        uint32_t last = 0;
+        if (lane == 0) last = atomicAdd(a.counters + cnt_base + node, 1u) == size - 1 ? 1u : 0u;
+        if (!__shfl_sync(0xffffffffu, last, 0)) return;
+        __threadfence();
+        if (lane == 0) a.counters[cnt_base + node] = 0;  // ready for the next launch
+        const float* p0 = a.partials + (size_t)(part_base + first) * PART_STRIDE;
+        const float* ml = p0 + 8 * D;
+        // Maxima and row sums of the node's entries: lane = (entry, head), one round of loads.
+        float M = -INFINITY, L = 0.f;
+        {
+            float mv[MERGE_FAN / 4 > 0 ? (MERGE_FAN + 3) / 4 : 1], lv[(MERGE_FAN + 3) / 4];
 #pragma unroll
-    for (int j = 0; j < NJ; j++) {
-        const uint32_t i = lane + j * 32, hh = i / (D / 4);
-        acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        Mh[j] = __shfl_sync(0xffffffffu, M, hh);
-        Lh[j] = __shfl_sync(0xffffffffu, L, hh);
-        off[j] = hh * D + (i % (D / 4)) * 4;
-    }
-    for (uint32_t c = 0; c < it.nch; c += 2) {
-        const bool two = c + 1 < it.nch;
-        const float* pa = p0 + (size_t)c * PART_STRIDE;
-        const float* pb = two ? pa + PART_STRIDE : pa;
-        float4 va[NJ], vb[NJ];
-        float wa[NJ], wb[NJ];
+            for (int u = 0; u < (int)((MERGE_FAN + 3) / 4); u++) {
+                const uint32_t c = (lane >> 3) + 4 * u;
+                mv[u] = c < size ? __ldcg(ml + (size_t)c * PART_STRIDE + hl) : -INFINITY;
+                lv[u] = c < size ? __ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < (int)((MERGE_FAN + 3) / 4); u++) M = fmaxf(M, mv[u]);
+            M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
+            M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
+#pragma unroll
+            for (int u = 0; u < (int)((MERGE_FAN + 3) / 4); u++) L = fmaf(lv[u], ex2(mv[u] - M), L);
+            L += __shfl_xor_sync(0xffffffffu, L, 8);
+            L += __shfl_xor_sync(0xffffffffu, L, 16);
+        }
+        // Output i = lane + 32 j of the 8 x D/4 float4 values; all of a lane's outputs advance
+        // together, two entries at a time: 2 * NJ 16-byte loads in flight per lane.
+        float4 acc[NJ];
+        float Mh[NJ], Lh[NJ];
+        uint32_t off[NJ];
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
-            const uint32_t hh = (lane + j * 32) / (D / 4);
-            va[j] = __ldcg(reinterpret_cast<const float4*>(pa + off[j]));
-            vb[j] = __ldcg(reinterpret_cast<const float4*>(pb + off[j]));
-            wa[j] = __ldcg(pa + 8 * D + hh);
-            wb[j] = __ldcg(pb + 8 * D + hh);
+            const uint32_t i = lane + j * 32, hh = i / (D / 4);
+            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+            Mh[j] = __shfl_sync(0xffffffffu, M, hh);
+            Lh[j] = __shfl_sync(0xffffffffu, L, hh);
+            off[j] = hh * D + (i % (D / 4)) * 4;
         }
+        for (uint32_t c = 0; c < size; c += 2) {
+            const bool two = c + 1 < size;
+            const float* pa = p0 + (size_t)c * PART_STRIDE;
+            const float* pb = two ? pa + PART_STRIDE : pa;
+            float4 va[NJ], vb[NJ];
+            float wa[NJ], wb[NJ];
 #pragma unroll
-        for (int j = 0; j < NJ; j++) {
-            const float ga = ex2(wa[j] - Mh[j]), gb = two ? ex2(wb[j] - Mh[j]) : 0.f;
-            acc[j].x = fmaf(va[j].x, ga, acc[j].x); acc[j].y = fmaf(va[j].y, ga, acc[j].y);
-            acc[j].z = fmaf(va[j].z, ga, acc[j].z); acc[j].w = fmaf(va[j].w, ga, acc[j].w);
-            acc[j].x = fmaf(vb[j].x, gb, acc[j].x); acc[j].y = fmaf(vb[j].y, gb, acc[j].y);
-            acc[j].z = fmaf(vb[j].z, gb, acc[j].z); acc[j].w = fmaf(vb[j].w, gb, acc[j].w);
+            for (int j = 0; j < NJ; j++) {
+                const uint32_t hh = (lane + j * 32) / (D / 4);
+                va[j] = __ldcg(reinterpret_cast<const float4*>(pa + off[j]));
+                vb[j] = __ldcg(reinterpret_cast<const float4*>(pb + off[j]));
+                wa[j] = __ldcg(pa + 8 * D + hh);
+                wb[j] = __ldcg(pb + 8 * D + hh);
+            }
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const float ga = ex2(wa[j] - Mh[j]), gb = two ? ex2(wb[j] - Mh[j]) : 0.f;
+                acc[j].x = fmaf(va[j].x, ga, acc[j].x); acc[j].y = fmaf(va[j].y, ga, acc[j].y);
+                acc[j].z = fmaf(va[j].z, ga, acc[j].z); acc[j].w = fmaf(va[j].w, ga, acc[j].w);
+                acc[j].x = fmaf(vb[j].x, gb, acc[j].x); acc[j].y = fmaf(vb[j].y, gb, acc[j].y);
+                acc[j].z = fmaf(vb[j].z, gb, acc[j].z); acc[j].w = fmaf(vb[j].w, gb, acc[j].w);
+            }
         }
-    }
+        if (n <= MERGE_FAN) {
+            // The root: the sequence's output.
 #pragma unroll
-    for (int j = 0; j < NJ; j++) {
-        const uint32_t hh = (lane + j * 32) / (D / 4);
-        if (hh < it.nheads)
-            *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0) * D + off[j]) =
-                make_float4(acc[j].x / Lh[j], acc[j].y / Lh[j], acc[j].z / Lh[j], acc[j].w / Lh[j]);
+            for (int j = 0; j < NJ; j++) {
+                const uint32_t hh = (lane + j * 32) / (D / 4);
+                if (hh < it.nheads)
+                    *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0) * D + off[j]) =
+                        make_float4(acc[j].x / Lh[j], acc[j].y / Lh[j], acc[j].z / Lh[j], acc[j].w / Lh[j]);
+            }
+            return;
+        }
+        // An entry of the next level, in the same form as a chunk's partial.
+        const uint32_t next_base = part_base + n;
+        float* pn = a.partials + (size_t)(next_base + node) * PART_STRIDE;
+#pragma unroll
+        for (int j = 0; j < NJ; j++) *reinterpret_cast<float4*>(pn + off[j]) = acc[j];
+        if (lane < 8) { pn[8 * D + lane] = M; pn[8 * D + 8 + lane] = L; }
+        cnt_base += (n + MERGE_FAN - 1) / MERGE_FAN;
+        part_base = next_base;
+        n = (n + MERGE_FAN - 1) / MERGE_FAN;
+        idx = node;
     }
-    if (lane == 0) a.counters[it.counter] = 0;  // ready for the next launch
 }
 
 template <int DT, int D, bool PRECISE>
@@ -397,14 +435,14 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             if (!__all_sync(0xffffffffu, mbar_wait(mfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;  // the abort path
             Mail m;
             m.seq = mailbox[ms].seq; m.head0 = mailbox[ms].head0; m.nheads = mailbox[ms].nheads; m.part0 = mailbox[ms].part0;
-            m.nch = mailbox[ms].nch; m.counter = mailbox[ms].counter; m.stop = mailbox[ms].stop;
+            m.nch = mailbox[ms].nch; m.counter = mailbox[ms].counter; m.stop = mailbox[ms].stop; m.chunk = mailbox[ms].chunk;
             __syncwarp();
             if (lane == 0) mbar_arrive(mfree0 + ms * 8);
 #ifdef QVX_TRACE
             if (lane == 0) TRACE(tp, m.stop ? 12 : 10);  // mail taken / stop
 #endif
             if (m.stop) return;
-            deliver<D>(a, m, lane);
+            deliver<D>(a, m, m.chunk, lane);
 #ifdef QVX_TRACE
             if (lane == 0) TRACE(tp, 11);  // deliver done
 #endif
@@ -624,6 +662,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             } else if (lane == 0) {
                 mailbox[ms].seq = it.seq; mailbox[ms].head0 = it.head0; mailbox[ms].nheads = it.nheads;
                 mailbox[ms].part0 = it.part0; mailbox[ms].nch = it.nch; mailbox[ms].counter = it.counter; mailbox[ms].stop = 0;
+                mailbox[ms].chunk = it.part - it.part0;
             }
         }
         __syncwarp();
@@ -654,9 +693,11 @@ bool attn_stream_supported(const Layout& L, size_t heads) {
     return L.d == 64 || L.d == 128 || L.d == 256;
 }
 
-// Floats of scratch one partial result takes.
+// Floats of scratch one partial result takes; partial slots and arrival counters a split
+// (sequence, group) of `nch` chunks takes (the merge tree's entries and nodes).
 size_t attn_stream_partial_floats(uint32_t d) { return 8 * (size_t)d + 16; }
-uint32_t attn_stream_counters_per_group() { return 1; }
+uint32_t attn_stream_parts(uint32_t nch) { return merge_entries_total(nch); }
+uint32_t attn_stream_counters(uint32_t nch) { return merge_counters_total(nch); }
 
 template <int DT, int D, bool PRECISE>
 static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t s) {

@@ -188,14 +188,21 @@ static cudaEvent_t next_event(DeviceExtras* x) {
 }
 
 // ---- tables ----------------------------------------------------------------------------------
-static uint32_t chunk_tokens_for(const Layout& L) {
+// The chunk a sequence of `len` positions is split into: a function of its own length and of
+// constants only (never of the batch or the device), so its result is the same whatever shares
+// the op.  512 positions, doubled (to at most 2048) while the sequence would still make more
+// than 32 chunks: long contexts get fewer, larger items and a shallower merge tree.
+// QVX_CHUNK_TOKENS fixes the size instead (experiments).
+static uint32_t chunk_tokens_for(const Layout& L, uint32_t len) {
     static const uint32_t configured = [] {
         const char* v = getenv("QVX_CHUNK_TOKENS");
         long n = v ? atol(v) : 0;
-        return (uint32_t)(n > 0 ? n : 512);
+        return (uint32_t)(n > 0 ? n : 0);
     }();
-    uint32_t c = std::max(configured, L.B) / L.B * L.B;
+    uint32_t c = std::max(configured ? configured : 512u, L.B) / L.B * L.B;
     while (c > 2048 && c > L.B) c -= L.B;
+    if (!configured)
+        while ((len + c - 1) / c > 32 && c * 2 <= 2048) c *= 2;
     return c;
 }
 
@@ -235,18 +242,22 @@ static int32_t validate_tables(qvx_device* dev, const Layout& L, size_t pool_blo
 static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint32_t* pos, size_t n_blocks,
                              bool split) {
     TableImage im{};
-    uint32_t chunk = chunk_tokens_for(L);
-    im.chunk_blocks = chunk / L.B;
-    im.item_words = (QVX_ITEM_HEADER_WORDS + im.chunk_blocks + 3u) & ~3u;
     size_t group = heads / L.kvh, groups = L.kvh * ((group + 7) / 8);
+    im.chunk_blocks = 1;
     for (size_t t = 0; t < s; t++) {
         im.max_pos = std::max(im.max_pos, pos[t]);
         if (!split) continue;
+        const uint32_t chunk = chunk_tokens_for(L, pos[t] + 1u);
+        im.chunk_blocks = std::max(im.chunk_blocks, chunk / L.B);
         size_t nch = ((size_t)pos[t] + chunk) / chunk;
         im.max_nch = std::max<size_t>(im.max_nch, nch);
         im.n_items += nch * groups;
-        if (nch > 1) { im.n_parts += nch * groups; im.n_counters += groups * attn_counters_per_group(L); }
+        if (nch > 1) {
+            im.n_parts += (size_t)attn_parts_per_group(L, (uint32_t)nch) * groups;
+            im.n_counters += (size_t)attn_counters_per_group(L, (uint32_t)nch) * groups;
+        }
     }
+    im.item_words = (QVX_ITEM_HEADER_WORDS + im.chunk_blocks + 3u) & ~3u;
     size_t off = 0;
     im.off_pos = off; off += 4 * s;
     im.off_table_at = off; off += 4 * s;
@@ -263,7 +274,7 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     memcpy(img + im.off_table_at, table_at, 4 * s);
     memcpy(img + im.off_blocks, blocks, 4 * n_blocks);
     if (im.n_items == 0) return;
-    const uint32_t chunk = im.chunk_blocks * L.B;
+    const uint32_t max_chunk = im.chunk_blocks * L.B;
     const uint32_t group = (uint32_t)(heads / L.kvh), gpk = (group + 7) / 8, groups = L.kvh * gpk;
     // Longest first, so the short tails fill the end of the launch.  The order is a function
     // of the lengths alone: a counting sort by tokens, ties in (sequence, group, chunk) order.
@@ -271,25 +282,24 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     std::vector<Key> keys;
     keys.reserve(im.n_items);
     std::vector<uint32_t> part_base(s), counter_base(s);
-    const uint32_t cpg = attn_counters_per_group(L);
     uint32_t part = 0, counter = 0;
     for (size_t t = 0; t < s; t++) {
-        uint32_t len = pos[t] + 1u, nch = (len + chunk - 1) / chunk;
+        const uint32_t len = pos[t] + 1u, chunk = chunk_tokens_for(L, len), nch = (len + chunk - 1) / chunk;
         part_base[t] = part; counter_base[t] = counter;
-        if (nch > 1) { part += nch * groups; counter += groups * cpg; }
+        if (nch > 1) { part += attn_parts_per_group(L, nch) * groups; counter += attn_counters_per_group(L, nch) * groups; }
         for (uint32_t grp = 0; grp < groups; grp++)
             for (uint32_t c = 0; c < nch; c++) keys.push_back(Key{std::min(chunk, len - c * chunk), (uint32_t)t, grp, c});
     }
     // (a counting sort: tokens <= chunk, and this runs once per op on the host's critical path)
-    std::vector<uint32_t> start(chunk + 2, 0);
-    for (const Key& k : keys) start[chunk - k.tokens + 1]++;
-    for (uint32_t v = 0; v <= chunk; v++) start[v + 1] += start[v];
+    std::vector<uint32_t> start(max_chunk + 2, 0);
+    for (const Key& k : keys) start[max_chunk - k.tokens + 1]++;
+    for (uint32_t v = 0; v <= max_chunk; v++) start[v + 1] += start[v];
     std::vector<uint32_t> order(keys.size());
-    for (uint32_t i = 0; i < keys.size(); i++) order[start[chunk - keys[i].tokens]++] = i;
+    for (uint32_t i = 0; i < keys.size(); i++) order[start[max_chunk - keys[i].tokens]++] = i;
     uint32_t* items = (uint32_t*)(img + im.off_items);
     for (size_t n = 0; n < keys.size(); n++) {
         const Key& k = keys[order[n]];
-        uint32_t t = k.seq, len = pos[t] + 1u, nch = (len + chunk - 1) / chunk;
+        const uint32_t t = k.seq, len = pos[t] + 1u, chunk = chunk_tokens_for(L, len), nch = (len + chunk - 1) / chunk;
         uint32_t kvh = k.grp / gpk, sub = k.grp % gpk;
         uint32_t* w = items + n * im.item_words;
         qvx_item_header h;
@@ -297,13 +307,13 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
         h.tokens = k.tokens;
         h.head0 = kvh * group + sub * 8;
         h.nheads_kv = std::min(8u, group - sub * 8) | (kvh << 16);
-        h.part0 = nch > 1 ? part_base[t] + k.grp * nch : 0xffffffffu;
+        h.part0 = nch > 1 ? part_base[t] + k.grp * attn_parts_per_group(L, nch) : 0xffffffffu;
         h.part = nch > 1 ? h.part0 + k.c : 0xffffffffu;
         h.nch = nch;
-        h.counter = nch > 1 ? counter_base[t] + k.grp * cpg : 0;  // the group's first arrival counter
+        h.counter = nch > 1 ? counter_base[t] + k.grp * attn_counters_per_group(L, nch) : 0;  // the group's first arrival counter
         memcpy(w, &h, sizeof h);
         uint32_t count = (k.tokens + L.B - 1) / L.B;
-        const uint32_t* src = blocks + table_at[t] + (size_t)k.c * im.chunk_blocks;
+        const uint32_t* src = blocks + table_at[t] + (size_t)k.c * (chunk / L.B);
         for (uint32_t b = 0; b < im.item_words - QVX_ITEM_HEADER_WORDS; b++) w[QVX_ITEM_HEADER_WORDS + b] = b < count ? src[b] : 0;
     }
 }

@@ -225,5 +225,6 @@ int32_t launch_attn_exact(qvx_device* dev, qvx_tables* t, const void* pool, cons
                           cudaStream_t s);
 size_t attn_partial_floats(const qvx_tables* t);  // floats of scratch the split kernel needs
 bool attn_split_supported(const Layout& L, size_t heads);
-uint32_t attn_counters_per_group(const Layout& L);
+uint32_t attn_parts_per_group(const Layout& L, uint32_t nch);
+uint32_t attn_counters_per_group(const Layout& L, uint32_t nch);
 }  // namespace qvx
