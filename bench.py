@@ -276,13 +276,20 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     oh = [torch.empty((s, heads, d), pin_memory=True) for _ in range(layers)]
     h2d = d2h = 0
 
+    # raw addresses once: the buffers live for the whole run
+    p_q, p_k, p_v, p_ta, p_geo = ptr(qh), ptr(kh), ptr(vh), ptr(table_at), C.byref(geo)
+    p_blocks, p_out = [ptr(b) for b in layer_blocks], [ptr(o) for o in oh]
+    host_call = lib.qvx_paged_attention_host_async
+
     def step_host(t: int):
         nonlocal h2d, d2h
         pos = (lengths + t).astype(np.uint32)
+        p_pos = ptr(pos)
         for l in range(layers):
-            dev.check(lib.qvx_paged_attention_host_async(dev.h, pool.handle, C.byref(geo), heads, s, ptr(qh), ptr(kh), ptr(vh), ptr(pos),
-                                                         ptr(layer_blocks[l]), blocks_per_layer, ptr(table_at), None, None, 0, ptr(oh[l]),
-                                                         qd.ATTN_AUTO))
+            rc = host_call(dev.h, pool.handle, p_geo, heads, s, p_q, p_k, p_v, p_pos, p_blocks[l], blocks_per_layer, p_ta, None, None, 0,
+                           p_out[l], qd.ATTN_AUTO)
+            if rc:
+                dev.check(rc)
         dev.wait()
         h2d = layers * (qh.numel() * 4 + kh.numel() * 8 + pos.nbytes + table_at.nbytes + layer_blocks[0].nbytes)
         d2h = layers * oh[0].numel() * 4

@@ -239,8 +239,42 @@ static int32_t validate_tables(qvx_device* dev, const Layout& L, size_t pool_blo
     return QVX_OK;
 }
 
+// The last op's work list, kept per device: the layers of one decode step come one after the
+// other with the same positions, so everything but the block ids is the same 48 times over.
+struct PlanCache {
+    bool valid = false;
+    uint32_t B = 0, kvh = 0, d = 0, dtype = 0, layout = 0;
+    size_t heads = 0, s = 0;
+    bool split = false;
+    std::vector<uint32_t> pos;
+    TableImage im{};                       // counts and sizes; the offsets depend on n_blocks and are redone
+    std::vector<qvx_item_header> headers;  // in launch order
+    std::vector<uint32_t> seq_off, count;  // per item: first block's offset in its sequence's table, blocks
+};
+
+static bool plan_hit(const PlanCache* c, const Layout& L, size_t heads, size_t s, const uint32_t* pos, bool split) {
+    return c && c->valid && c->B == L.B && c->kvh == L.kvh && c->d == L.d && c->dtype == L.dtype && c->layout == L.layout &&
+           c->heads == heads && c->s == s && c->split == split && memcmp(c->pos.data(), pos, 4 * s) == 0;
+}
+
+static void image_offsets(TableImage& im, size_t s, size_t n_blocks) {
+    size_t off = 0;
+    im.off_pos = off; off += 4 * s;
+    im.off_table_at = off; off += 4 * s;
+    im.off_blocks = off; off += 4 * n_blocks;
+    off = (off + 15) & ~(size_t)15;
+    im.off_items = off; off += 4ull * im.item_words * im.n_items;
+    im.bytes = (off + 255) & ~(size_t)255;
+}
+
 static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint32_t* pos, size_t n_blocks,
-                             bool split) {
+                             bool split, PlanCache* cache = nullptr) {
+    if (plan_hit(cache, L, heads, s, pos, split)) {
+        TableImage im = cache->im;
+        image_offsets(im, s, n_blocks);
+        return im;
+    }
+    if (cache) cache->valid = false;
     TableImage im{};
     size_t group = heads / L.kvh, groups = L.kvh * ((group + 7) / 8);
     im.chunk_blocks = 1;
@@ -258,22 +292,37 @@ static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint
         }
     }
     im.item_words = (QVX_ITEM_HEADER_WORDS + im.chunk_blocks + 3u) & ~3u;
-    size_t off = 0;
-    im.off_pos = off; off += 4 * s;
-    im.off_table_at = off; off += 4 * s;
-    im.off_blocks = off; off += 4 * n_blocks;
-    off = (off + 15) & ~(size_t)15;
-    im.off_items = off; off += 4ull * im.item_words * im.n_items;
-    im.bytes = (off + 255) & ~(size_t)255;
+    image_offsets(im, s, n_blocks);
     return im;
 }
 
 static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size_t heads, size_t s,
-                       const uint32_t* pos, const uint32_t* blocks, size_t n_blocks, const uint32_t* table_at) {
+                       const uint32_t* pos, const uint32_t* blocks, size_t n_blocks, const uint32_t* table_at,
+                       PlanCache* cache = nullptr, bool split = true) {
     memcpy(img + im.off_pos, pos, 4 * s);
     memcpy(img + im.off_table_at, table_at, 4 * s);
     memcpy(img + im.off_blocks, blocks, 4 * n_blocks);
     if (im.n_items == 0) return;
+    const uint32_t id_words = im.item_words - QVX_ITEM_HEADER_WORDS;
+    if (plan_hit(cache, L, heads, s, pos, split)) {
+        uint32_t* items = (uint32_t*)(img + im.off_items);
+        for (size_t n = 0; n < cache->headers.size(); n++) {
+            uint32_t* w = items + n * im.item_words;
+            memcpy(w, &cache->headers[n], sizeof(qvx_item_header));
+            const uint32_t* src = blocks + table_at[cache->headers[n].seq] + cache->seq_off[n];
+            const uint32_t count = cache->count[n];
+            memcpy(w + QVX_ITEM_HEADER_WORDS, src, 4 * count);
+            if (count < id_words) memset(w + QVX_ITEM_HEADER_WORDS + count, 0, 4 * (id_words - count));
+        }
+        return;
+    }
+    if (cache) {
+        cache->B = L.B; cache->kvh = L.kvh; cache->d = L.d; cache->dtype = L.dtype; cache->layout = L.layout;
+        cache->heads = heads; cache->s = s; cache->split = split;
+        cache->pos.assign(pos, pos + s);
+        cache->im = im;
+        cache->headers.resize(im.n_items); cache->seq_off.resize(im.n_items); cache->count.resize(im.n_items);
+    }
     const uint32_t max_chunk = im.chunk_blocks * L.B;
     const uint32_t group = (uint32_t)(heads / L.kvh), gpk = (group + 7) / 8, groups = L.kvh * gpk;
     // Longest first, so the short tails fill the end of the launch.  The order is a function
@@ -314,8 +363,10 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
         memcpy(w, &h, sizeof h);
         uint32_t count = (k.tokens + L.B - 1) / L.B;
         const uint32_t* src = blocks + table_at[t] + (size_t)k.c * (chunk / L.B);
-        for (uint32_t b = 0; b < im.item_words - QVX_ITEM_HEADER_WORDS; b++) w[QVX_ITEM_HEADER_WORDS + b] = b < count ? src[b] : 0;
+        for (uint32_t b = 0; b < id_words; b++) w[QVX_ITEM_HEADER_WORDS + b] = b < count ? src[b] : 0;
+        if (cache) { cache->headers[n] = h; cache->seq_off[n] = k.c * (chunk / L.B); cache->count[n] = count; }
     }
+    if (cache) cache->valid = true;
 }
 
 static void bind_image(qvx_tables* t, const TableImage& im, void* dmem) {
@@ -458,6 +509,7 @@ void qvx_close(qvx_device* dev) {
         dev->inflight_tables.clear();
     }
     for (cudaEvent_t ev : dev->event_pool) cudaEventDestroy(ev);
+    delete static_cast<PlanCache*>(dev->plan_cache);
     if (dev->partials) cudaFree(dev->partials);
     if (dev->counters) cudaFree(dev->counters);
     if (dev->queue) cudaFree(dev->queue);
@@ -722,7 +774,9 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     const size_t kv_out = (size_t)L.kvh * L.d, q_out = heads * L.d;
     const bool split = attn_split_supported(L, heads) && (variant & 0xffu) != QVX_ATTN_EXACT;
     variant &= 0xffu;  // the host op orders its own copies and kernels: no overlap with what precedes it
-    TableImage im = plan_image(L, heads, s, pos, n_blocks, split);
+    if (!dev->plan_cache) dev->plan_cache = new PlanCache;
+    PlanCache* cache = static_cast<PlanCache*>(dev->plan_cache);
+    TableImage im = plan_image(L, heads, s, pos, n_blocks, split, cache);
     if (im.max_nch > MAX_CHUNKS) return too_many_chunks(dev, im.max_nch);
     // Staged on the device for this op: the tables image, sync_to, q, k_new, v_new, sync rows, out.
     auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
@@ -743,7 +797,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     uint8_t* hs = (uint8_t*)dev->staging + base;
     uint8_t* ds = (uint8_t*)dev->dstaging + base;
 
-    fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at);
+    fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at, cache, split);
     // A position listed twice: the later row wins (the reference writes them in list order).
     uint32_t* st = (uint32_t*)(hs + o_syncto);
     {

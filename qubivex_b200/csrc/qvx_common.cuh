@@ -154,6 +154,7 @@ struct qvx_device {
     // The scratch comes twice: consecutive launches alternate halves, so that a launch allowed to
     // overlap the tail of the one before never shares partials, counters or queue with it.
     uint32_t scratch_half = 0;
+    void* plan_cache = nullptr;  // the last host op's work list (PlanCache, qvx_api.cu)
     // Pinned staging for the _host calls, grown on demand; `staging_used` is reset by qvx_wait.
     char* staging = nullptr;
     size_t staging_cap = 0, staging_used = 0;

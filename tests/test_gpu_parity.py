@@ -316,3 +316,28 @@ def test_layers_back_to_back_with_the_pool_settled_flag_give_the_same_bits(dev):
     got_out, got_pool = run(qd.ATTN_POOL_SETTLED, False)
     assert np.array_equal(got_pool, want_pool)
     assert np.array_equal(got_out.view(np.uint32), want_out.view(np.uint32))
+
+
+def test_a_work_list_kept_from_the_previous_layer_gives_the_same_bits(dev):
+    # The host op keeps its last work list: a second op with the same positions (the next layer:
+    # other blocks, other rows) reuses it; other positions rebuild it.
+    lengths = [700, 33, 2047, 1200, 16]
+    a = Case(32, 4, 128, 16, "bf16", lengths, seed=71)
+    b = Case(32, 4, 128, 16, "bf16", lengths, seed=72)
+    nb = (b.lengths + 15) // 16  # its tables laid out in the opposite order
+    b.table_at = (np.concatenate([[0], np.cumsum(nb[::-1])[:-1]])[::-1]).astype(np.uint32)
+    sync_to = []
+    for t in range(len(lengths)):
+        for p in range(int(b.pos[t])):
+            sync_to.append(int(b.blocks[b.table_at[t] + p // 16]) * 16 + p % 16)
+    b.sync_to = np.array(sync_to, dtype=np.uint32)
+    other = Case(32, 4, 128, 16, "bf16", [5, 900], seed=73)
+    _, want_b = b.run_oracle()
+    a.run_device(dev, variant=qd.ATTN_SPLIT)
+    pool_hit, out_hit = b.run_device(dev, variant=qd.ATTN_SPLIT)      # same positions as a: reuse
+    other.run_device(dev, variant=qd.ATTN_SPLIT)
+    pool_miss, out_miss = b.run_device(dev, variant=qd.ATTN_SPLIT)    # after other positions: rebuilt
+    assert np.array_equal(out_hit.view(np.uint32), out_miss.view(np.uint32))
+    assert np.array_equal(pool_hit, pool_miss)
+    ok, err = within(out_hit, want_b, "bf16")
+    assert ok, err
