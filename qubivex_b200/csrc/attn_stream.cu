@@ -702,7 +702,8 @@ uint32_t attn_stream_counters(uint32_t nch) { return merge_counters_total(nch); 
 template <int DT, int D, bool PRECISE>
 static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t s) {
     auto kernel = attn_stream_kernel<DT, D, PRECISE>;
-    static thread_local int ctas_per_sm = 0;
+    static int per_device[64] = {};  // set up once per device (the attribute belongs to the device's context)
+    int& ctas_per_sm = per_device[dev->ordinal & 63];
     if (!ctas_per_sm) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamSmem<D>::total);
         if (e == cudaSuccess)

@@ -9,6 +9,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <deque>
 #include <unordered_set>
 
 #include "qvx_common.cuh"
@@ -77,12 +78,22 @@ static void drain_timers(qvx_device* dev) {
 }
 
 // The status word lives in mapped pinned memory: kernels write it, the host reads it with no copy.
+// A host op in flight: its slice of the staging ring, its tables, and the three events that order
+// its copies in, its kernels and its copy out.  `out_done` says the slice may be reused.
+struct HostOp {
+    size_t begin = 0, end = 0;
+    qvx_tables* tables = nullptr;
+    cudaEvent_t in_done = nullptr, kernels_done = nullptr, out_done = nullptr;
+};
+
 struct DeviceExtras {
     int* status_host = nullptr;
     int* status_dev = nullptr;
     cudaStream_t h2d = nullptr, d2h = nullptr;
-    std::vector<cudaEvent_t> sync_events;
-    size_t next_event = 0;
+    std::vector<cudaEvent_t> sync_events;  // spare events, handed to ops and taken back
+    std::deque<HostOp> ops;                // oldest first
+    size_t ring_head = 0;                  // where the next op's slice starts
+    bool ring_was_short = false;           // an op had to wait for a slice: grow at the next drain
 };
 static std::mutex g_extras_mu;
 static std::vector<std::pair<qvx_device*, DeviceExtras*>> g_extras;
@@ -142,14 +153,33 @@ static int32_t buffer_of(qvx_device* dev, qvx_buffer* b) {
 }
 
 // ---- staging for the host ops ---------------------------------------------------------------
-static int32_t ensure_staging(qvx_device* dev, size_t need) {
-    if (dev->staging_cap - dev->staging_used >= need && dev->dstaging_cap == dev->staging_cap) return QVX_OK;
-    return QVX_DECLINED;  // the caller drains the device and grows or resets
+// One pinned ring on the host and its twin on the device.  Each op takes a contiguous slice and
+// gives it back when its copy out has finished, so submitting runs ahead of the device by as many
+// ops as the ring holds and never has to drain it; an op that finds no room waits for the oldest
+// op only.  The ring starts small and grows fourfold (to RING_AUTO_MAX, or to one op's own need) at a
+// drain after an op had to wait.
+static const size_t RING_MIN = 32u << 20, RING_AUTO_MAX = 128u << 20;
+
+static cudaEvent_t take_event(DeviceExtras* x) {
+    if (x->sync_events.empty()) {
+        cudaEvent_t e = nullptr;
+        cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+        return e;
+    }
+    cudaEvent_t e = x->sync_events.back();
+    x->sync_events.pop_back();
+    return e;
 }
 
-static int32_t grow_staging(qvx_device* dev, size_t need) {
+static void retire(qvx_device* dev, DeviceExtras* x, HostOp& op) {
+    (void)dev;
+    delete op.tables;
+    for (cudaEvent_t e : {op.in_done, op.kernels_done, op.out_done})
+        if (e) x->sync_events.push_back(e);
+}
+
+static int32_t resize_staging(qvx_device* dev, size_t cap) {
     // Only called with nothing in flight.
-    size_t cap = std::max<size_t>(need, std::max<size_t>(dev->staging_cap * 2, 8u << 20));
     if (dev->staging) cudaFreeHost(dev->staging);
     if (dev->dstaging) cudaFree(dev->dstaging);
     dev->staging = nullptr; dev->dstaging = nullptr; dev->staging_cap = dev->dstaging_cap = 0;
@@ -158,7 +188,6 @@ static int32_t grow_staging(qvx_device* dev, size_t need) {
     e = cudaMalloc((void**)&dev->dstaging, cap);
     if (e != cudaSuccess) return check_cuda(dev, e, "device staging");
     dev->staging_cap = dev->dstaging_cap = cap;
-    dev->staging_used = 0;
     return QVX_OK;
 }
 
@@ -170,21 +199,50 @@ static int32_t wait_locked(qvx_device* dev) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(x->d2h);
     dev->xfer.wait_ns += now_ns() - t0;
     dev->xfer.fence_waits++;
+    for (HostOp& op : x->ops) retire(dev, x, op);
+    x->ops.clear();
+    x->ring_head = 0;
     dev->staging_used = 0;
-    x->next_event = 0;
-    for (qvx_tables* t : dev->inflight_tables) delete t;
-    dev->inflight_tables.clear();
     if (e != cudaSuccess) return check_cuda(dev, e, "wait");
+    if (x->ring_was_short && dev->staging_cap && dev->staging_cap < RING_AUTO_MAX) {
+        x->ring_was_short = false;
+        int32_t rc = resize_staging(dev, std::min(dev->staging_cap * 4, RING_AUTO_MAX));
+        if (rc) return rc;
+    }
     return check_status(dev);
 }
 
-static cudaEvent_t next_event(DeviceExtras* x) {
-    if (x->next_event == x->sync_events.size()) {
-        cudaEvent_t e;
-        cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
-        x->sync_events.push_back(e);
+// A slice of `need` bytes (a multiple of 256) for a new op; *begin is its offset in both rings.
+static int32_t take_slice(qvx_device* dev, DeviceExtras* x, size_t need, size_t* begin) {
+    if (need > dev->staging_cap) {
+        int32_t rc = wait_locked(dev);
+        if (rc) return rc;
+        if (need > dev->staging_cap) {  // the drain itself may have grown the ring
+            rc = resize_staging(dev, std::max(need, std::max(dev->staging_cap * 2, RING_MIN)));
+            if (rc) return rc;
+        }
     }
-    return x->sync_events[x->next_event++];
+    const size_t cap = dev->staging_cap;
+    for (;;) {
+        if (x->ops.empty()) { x->ring_head = 0; *begin = 0; break; }
+        const size_t head = x->ring_head, tail = x->ops.front().begin;
+        // Never fill the ring to the last byte: head == tail then always means "empty".
+        if (head >= tail) {
+            if (cap - head >= need) { *begin = head; break; }
+            if (tail > need) { *begin = 0; break; }
+        } else if (tail - head > need) { *begin = head; break; }
+        // No room: the oldest op's slice comes back when its copy out is done.
+        uint64_t t0 = now_ns();
+        cudaError_t e = cudaEventSynchronize(x->ops.front().out_done);
+        dev->xfer.wait_ns += now_ns() - t0;
+        x->ring_was_short = true;
+        if (e != cudaSuccess) return check_cuda(dev, e, "wait for a staging slice");
+        retire(dev, x, x->ops.front());
+        x->ops.pop_front();
+    }
+    x->ring_head = *begin + need;
+    dev->staging_used = x->ring_head;
+    return QVX_OK;
 }
 
 // ---- tables ----------------------------------------------------------------------------------
@@ -505,8 +563,10 @@ void qvx_close(qvx_device* dev) {
     {
         std::lock_guard<std::mutex> lk(dev->mu);
         drain_timers(dev);
-        for (qvx_tables* t : dev->inflight_tables) delete t;
-        dev->inflight_tables.clear();
+        if (DeviceExtras* x = extras(dev)) {
+            for (HostOp& op : x->ops) retire(dev, x, op);
+            x->ops.clear();
+        }
     }
     for (cudaEvent_t ev : dev->event_pool) cudaEventDestroy(ev);
     delete static_cast<PlanCache*>(dev->plan_cache);
@@ -783,19 +843,17 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     const size_t o_img = 0, o_syncto = o_img + im.bytes, o_q = o_syncto + up(4 * n_sync),
                  o_k = o_q + up(4 * s * q_out), o_v = o_k + up(4 * s * kv_out), o_sync = o_v + up(4 * s * kv_out),
                  o_out = o_sync + up(8 * n_sync * kv_out), total = o_out + up(4 * s * q_out);
-    if (ensure_staging(dev, total) != QVX_OK) {
-        rc = wait_locked(dev);
-        if (rc) return rc;
-        if (dev->staging_cap < total) {
-            rc = grow_staging(dev, total);
-            if (rc) return rc;
-        }
-    }
     DeviceExtras* x = extras(dev);
-    const size_t base = dev->staging_used;
-    dev->staging_used += total;
+    size_t base = 0;
+    rc = take_slice(dev, x, total, &base);
+    if (rc) return rc;
     uint8_t* hs = (uint8_t*)dev->staging + base;
     uint8_t* ds = (uint8_t*)dev->dstaging + base;
+    // From here on the op is in the list: whatever happens, its slice and tables go back at a drain.
+    x->ops.emplace_back();
+    HostOp& op = x->ops.back();
+    op.begin = base; op.end = base + total;
+    op.in_done = take_event(x); op.kernels_done = take_event(x); op.out_done = take_event(x);
 
     fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at, cache, split);
     // A position listed twice: the later row wins (the reference writes them in list order).
@@ -809,7 +867,8 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     t->dev = dev; t->L = L; t->pool_blocks = held; t->heads = heads; t->s = s; t->n_blocks = n_blocks;
     bind_image(t, im, ds + o_img);
     t->owns_dmem = false;
-    dev->inflight_tables.push_back(t);
+    op.tables = t;
+    cudaEventRecord(op.out_done, x->d2h);  // re-recorded after the copy out; a failed op's slice is free at once
     if (split) {
         rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
         if (rc) return rc;
@@ -827,9 +886,8 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     copy_in(o_v, v_new, 4 * s * kv_out);
     copy_in(o_sync, sync, 8 * n_sync * kv_out);
     if (e != cudaSuccess) return check_cuda(dev, e, "copy in");
-    cudaEvent_t ev_in = next_event(x);
-    cudaEventRecord(ev_in, h2d);
-    cudaStreamWaitEvent(cs, ev_in, 0);
+    cudaEventRecord(op.in_done, h2d);
+    cudaStreamWaitEvent(cs, op.in_done, 0);
 
     // sync rows, then the new rows, then attention: sim.rs:385-429.
     const float* d_sync = (const float*)(ds + o_sync);
@@ -839,14 +897,14 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
         rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), (float*)(ds + o_out), variant, cs,
                            (const float*)(ds + o_k), (const float*)(ds + o_v));
     if (rc) return rc;
-    cudaEvent_t ev_done = next_event(x);
-    cudaEventRecord(ev_done, cs);
-    cudaStreamWaitEvent(d2h, ev_done, 0);
+    cudaEventRecord(op.kernels_done, cs);
+    cudaStreamWaitEvent(d2h, op.kernels_done, 0);
     if (s) {
         e = cudaMemcpyAsync(out, ds + o_out, 4 * s * q_out, cudaMemcpyDeviceToHost, d2h);
         if (e != cudaSuccess) return check_cuda(dev, e, "copy out");
     }
-    // The next op's copies may overwrite nothing this op reads: each op has its own staging.
+    cudaEventRecord(op.out_done, d2h);
+    // A later op's copies overwrite nothing this op reads: its slice is its own until out_done.
     dev->xfer.submissions++;
     dev->xfer.activations_in += in_bytes;
     dev->xfer.activations_out += 4 * s * q_out;

@@ -155,12 +155,11 @@ struct qvx_device {
     // overlap the tail of the one before never shares partials, counters or queue with it.
     uint32_t scratch_half = 0;
     void* plan_cache = nullptr;  // the last host op's work list (PlanCache, qvx_api.cu)
-    // Pinned staging for the _host calls, grown on demand; `staging_used` is reset by qvx_wait.
+    // Pinned staging ring for the _host calls and its device twin; the ops in flight hold slices.
     char* staging = nullptr;
     size_t staging_cap = 0, staging_used = 0;
-    char* dstaging = nullptr;  // its device twin
+    char* dstaging = nullptr;
     size_t dstaging_cap = 0;
-    std::vector<qvx_tables*> inflight_tables;
     struct PendingOut { float* dst; const float* src; size_t bytes; };
     std::vector<PendingOut> pending_out;
 };

@@ -341,3 +341,27 @@ def test_a_work_list_kept_from_the_previous_layer_gives_the_same_bits(dev):
     assert np.array_equal(pool_hit, pool_miss)
     ok, err = within(out_hit, want_b, "bf16")
     assert ok, err
+
+
+def test_more_ops_in_flight_than_the_staging_ring_holds(dev):
+    # 40 ops of ~2.3 MiB staged bytes each, submitted without a wait: the ring gives slices back as
+    # the oldest ops finish.  Every op's output equals the same op run alone.
+    c = Case(32, 4, 128, 16, "bf16", [300] * 64, seed=81)
+    buf = dev.alloc(c.pool_blocks * c.bb)
+    try:
+        dev.write(buf, 0, c.host_pool())
+        first = dev.paged_attention(buf, c.geo_d, c.heads, c.q, c.k_new, c.v_new, c.pos, c.blocks, c.table_at, c.sync, c.sync_to,
+                                    variant=qd.ATTN_SPLIT)
+        qs = [np.ascontiguousarray(c.q * (1.0 + 0.01 * i)) for i in range(40)]
+        alone = [dev.paged_attention(buf, c.geo_d, c.heads, qs[i], c.k_new, c.v_new, c.pos, c.blocks, c.table_at, variant=qd.ATTN_SPLIT)
+                 for i in range(40)]
+        outs = [np.empty_like(first) for _ in range(40)]
+        for i in range(40):
+            dev.paged_attention(buf, c.geo_d, c.heads, qs[i], c.k_new, c.v_new, c.pos, c.blocks, c.table_at, out=outs[i],
+                                variant=qd.ATTN_SPLIT, wait=False)
+        dev.wait()
+        for i in range(40):
+            assert np.array_equal(outs[i].view(np.uint32), alone[i].view(np.uint32)), i
+        assert np.array_equal(alone[0].view(np.uint32), first.view(np.uint32))
+    finally:
+        buf.free()
