@@ -179,7 +179,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     bb = qd.block_bytes(geo)
     scale = wl.value_scale(shape)
     W, K = args.warmup, args.steps
-    We, Ke = min(W, 2), K
+    We, Ke = min(W, 3), K
     total_steps = W + K + We + Ke
     lengths = wl.contexts(shape, SEED + rank)            # positions prefilled per sequence
     nb_seq = (lengths + total_steps + B - 1) // B          # table entries per sequence, with room to grow
@@ -297,11 +297,14 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     for t in range(W + K, W + K + We):
         step_host(t)
     barrier()
+    each_ms = []
     t0 = time.perf_counter()
     for t in range(W + K + We, W + K + We + Ke):
         step_host(t)
+        each_ms.append(time.perf_counter())
     torch.cuda.synchronize()
     el = torch.tensor([time.perf_counter() - t0], device="cuda")
+    each_ms = [round(1e3 * (b - a), 3) for a, b in zip([t0] + each_ms[:-1], each_ms)]
     if dist is not None:
         dist.all_reduce(el, op=dist.ReduceOp.MAX)
     e2e_value = world * s * Ke / float(el.item())
@@ -322,7 +325,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                      "launch_us": attn_ns / max(attn_launches, 1) / 1e3, "launches_timed": int(attn_launches),
                      "kernels_us_per_launch": {k: (v[1] / v[0] / 1e3 if v[0] else 0.0) for k, v in kt.items() if v[0]}},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "call": "qvx_paged_attention_host_async x layers + qvx_wait per step"},
+                "call": "qvx_paged_attention_host_async x layers + qvx_wait per step", "ms_each_step": each_ms},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

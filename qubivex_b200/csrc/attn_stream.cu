@@ -51,9 +51,17 @@ namespace qvx {
 constexpr int CW = QVX_CW;
 constexpr int CT = CW * 32;                    // consumer threads
 constexpr int STREAM_THREADS = CT + 64;        // + the producer warp and the epilogue warp
-constexpr int MAIL_SLOTS = 4;
+constexpr int MAIL_SLOTS = 2;                  // one per buffer of consumer states
 constexpr int Q_SLOTS = 2;
 constexpr int REC_SLOTS = 4;
+#ifndef QVX_CLAIM_AHEAD
+#define QVX_CLAIM_AHEAD 8
+#endif
+#ifndef QVX_FETCH_AHEAD
+#define QVX_FETCH_AHEAD (QVX_CLAIM_AHEAD / 2)
+#endif
+constexpr uint32_t CLAIM_AHEAD = QVX_CLAIM_AHEAD;  // tiles before an item's end at which the producer claims the next item
+constexpr uint32_t FETCH_AHEAD = QVX_FETCH_AHEAD;  // ... and at which it asks for the item's record
 constexpr int REC_WORDS = 144;                 // header + up to 136 block ids
 
 struct StreamArgs {
@@ -92,7 +100,6 @@ __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; as
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory"); }
 
 template <int D>
 struct StreamSmem {
@@ -102,7 +109,7 @@ struct StreamSmem {
     static constexpr uint32_t stage_bytes = 2 * tile_bytes;
     static constexpr uint32_t q_stride = D * 4 + 16;  // padded rows: fragment reads hit 32 distinct banks
     static constexpr uint32_t res_floats = 16 + 8 * D;  // one warp's state: m[8], l[8], acc[8][D]
-    static constexpr uint32_t res_bytes = CW * res_floats * 4;
+    static constexpr uint32_t res_bytes = MAIL_SLOTS * CW * res_floats * 4;  // two items' worth: one being merged, one being filled
     static constexpr uint32_t q_bytes = Q_SLOTS * 8 * q_stride;
     static constexpr uint32_t rec_bytes = REC_SLOTS * REC_WORDS * 4;
     static constexpr uint32_t fixed = res_bytes + q_bytes + rec_bytes + 1024;
@@ -110,14 +117,18 @@ struct StreamSmem {
     // A multiple of CW: tile n goes to stage n % stages and to warp n % CW, so a stage is
     // always read by the same warp and a warp waits for its stages' phases strictly in order
     // (waiting two phases ahead on an mbarrier parity would return at once).
+#ifdef QVX_MAX_STAGES  // experiments: a shallower ring
+    static constexpr uint32_t stages = QVX_MAX_STAGES;
+#else
     static constexpr uint32_t stages = (stages_fit > 4 * CW ? 4 * CW : stages_fit) / CW * CW;
+#endif
     static constexpr uint32_t ring_off = 0;
     static constexpr uint32_t res_off = stages * stage_bytes;
     static constexpr uint32_t q_off = res_off + res_bytes;
     static constexpr uint32_t rec_off = q_off + q_bytes;
     static constexpr uint32_t bar_off = rec_off + rec_bytes;
     // full[stages], empty[stages], qfull[Q_SLOTS], qempty[Q_SLOTS], rec[REC_SLOTS],
-    // mail_full[MAIL_SLOTS], mail_free[MAIL_SLOTS], then the abort word and the mailbox
+    // res_full[MAIL_SLOTS], res_free[MAIL_SLOTS], then the abort word and the mailbox
     static constexpr uint32_t n_bars = 2 * stages + 2 * Q_SLOTS + REC_SLOTS + 2 * MAIL_SLOTS;
     static constexpr uint32_t abort_off = bar_off + n_bars * 8;
     static constexpr uint32_t mail_off = abort_off + 16;
@@ -125,7 +136,8 @@ struct StreamSmem {
     static_assert(stages >= CW, "the ring needs a stage per consumer warp");
 };
 
-// What the consumers tell the epilogue warp about a chunk whose partial they have stored.
+// What the consumers tell the epilogue warp about the item whose states they have left in a buffer.
+// `chunk` is the item's place among its sequence's chunks, NO_PART for a sequence in one piece.
 struct Mail {
     uint32_t seq, head0, nheads, part0, nch, counter, stop, chunk;
 };
@@ -264,7 +276,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     const uint32_t sbase = smem_u32(smem);
     const uint32_t full0 = sbase + SM::bar_off, empty0 = full0 + SM::stages * 8;
     const uint32_t qfull0 = empty0 + SM::stages * 8, qempty0 = qfull0 + Q_SLOTS * 8, recbar0 = qempty0 + Q_SLOTS * 8;
-    const uint32_t mfull0 = recbar0 + REC_SLOTS * 8, mfree0 = mfull0 + MAIL_SLOTS * 8;
+    const uint32_t rfull0 = recbar0 + REC_SLOTS * 8, rfree0 = rfull0 + MAIL_SLOTS * 8;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + SM::abort_off);
     volatile Mail* mailbox = reinterpret_cast<volatile Mail*>(smem + SM::mail_off);
 
@@ -277,7 +289,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         for (uint32_t s = 0; s < SM::stages; s++) { mbar_init(full0 + s * 8, 1); mbar_init(empty0 + s * 8, 1); }
         for (uint32_t s = 0; s < Q_SLOTS; s++) { mbar_init(qfull0 + s * 8, 1); mbar_init(qempty0 + s * 8, CW); }
         for (uint32_t s = 0; s < REC_SLOTS; s++) mbar_init(recbar0 + s * 8, 1);
-        for (uint32_t s = 0; s < MAIL_SLOTS; s++) { mbar_init(mfull0 + s * 8, CW); mbar_init(mfree0 + s * 8, 1); }
+        for (uint32_t s = 0; s < MAIL_SLOTS; s++) { mbar_init(rfull0 + s * 8, CW); mbar_init(rfree0 + s * 8, 1); }
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -302,19 +314,17 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 mbar_arrive(recbar0 + slot * 8);
             }
         };
-        uint32_t n = 0;          // tiles issued so far, over all items
+        // Lane 0 issues every tile, one after the other, and nothing hides what each costs it: the
+        // loop keeps running values (stage, parity, source address) instead of deriving them.
+        uint32_t st = 0, empty_parity = 1;  // the next tile's stage; the parity its `empty` barrier is waited on with
+        const bool one_copy = a.page_bytes == SM::tile_bytes;  // one tile per block: its values follow its keys
         bool failed = false, queue_dry = false;
 #ifdef QVX_TRACE
         const uint32_t trace_base = 0; uint32_t tp = 0;
         if (lane == 0) TRACE(tp, 1);   // producer start
 #endif
-        uint32_t idx_next = 0;
-        if (lane == 0) {
-            // The first item needs no atomic: CTA b starts with item b, the queue hands out the rest.
-            idx_next = blockIdx.x;
-            fetch(0, idx_next);
-            idx_next = gridDim.x + atomicAdd(a.queue, 1u);  // item 1: in flight while item 0 is set up
-        }
+        // The first item needs no atomic: CTA b starts with item b, the queue hands out the rest.
+        if (lane == 0) fetch(0, blockIdx.x);
         for (uint32_t k = 0;; k++) {
             const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
             // The consumers are done with the queries of item k - Q_SLOTS (and so with every
@@ -322,6 +332,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             bool ok = mbar_wait(recbar0 + rslot * 8, (k / REC_SLOTS) & 1);
             ok = ok && mbar_wait(qempty0 + qslot * 8, ((k / Q_SLOTS) & 1) ^ 1);
             if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, 5);  // record and query slot ready
+#endif
             const uint32_t* rec = rec_base + rslot * REC_WORDS;
             const uint32_t seq = rec[0], tokens = rec[1], head0 = rec[2], nheads = rec[3] & 0xffffu, kvh = rec[3] >> 16;
             if (tokens == 0) {
@@ -330,20 +343,28 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
             const uint8_t* base = a.pool + (uint64_t)kvh * 2u * a.page_bytes;
             const uint32_t ntiles = (tokens + TILE - 1) / TILE;
-            auto issue_tile = [&](uint32_t tau) -> bool {  // lane 0 only
-                const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
-                if (!mbar_wait(empty0 + st * 8, ph ^ 1)) return false;
-                const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + tau / a.tiles_per_block];
-                const uint8_t* src = base + (uint64_t)blk * a.block_bytes + (uint64_t)(tau % a.tiles_per_block) * SM::tile_bytes;
+            const uint32_t* ids = rec + QVX_ITEM_HEADER_WORDS;
+            const uint32_t nblk = (ntiles + a.tiles_per_block - 1) / a.tiles_per_block;
+            uint32_t bi = 0, bj = 0;  // the next tile: block of the item, tile of the block
+            const uint8_t* src = base + (uint64_t)ids[0] * a.block_bytes;
+            auto issue_tile = [&]() -> bool {  // lane 0 only: the item's next tile
+                const uint32_t eb = empty0 + st * 8, fb = full0 + st * 8;
+                if (!mbar_try_wait(eb, empty_parity) && !mbar_wait(eb, empty_parity)) return false;
                 const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
-                mbar_expect_tx(full0 + st * 8, SM::stage_bytes);
-                if (a.page_bytes == SM::tile_bytes) {  // one tile per block: its values follow its keys
-                    bulk_g2s(dst, src, SM::stage_bytes, full0 + st * 8);
+                mbar_expect_tx(fb, SM::stage_bytes);
+                if (one_copy) {
+                    bulk_g2s(dst, src, SM::stage_bytes, fb);
                 } else {
-                    bulk_g2s(dst, src, SM::tile_bytes, full0 + st * 8);
-                    bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, full0 + st * 8);
+                    bulk_g2s(dst, src, SM::tile_bytes, fb);
+                    bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, fb);
                 }
-                n++;
+                if (++st == SM::stages) { st = 0; empty_parity ^= 1u; }
+                if (++bj == a.tiles_per_block) {
+                    bj = 0;
+                    if (++bi < nblk) src = base + (uint64_t)ids[bi] * a.block_bytes;
+                } else {
+                    src += SM::tile_bytes;
+                }
                 return true;
             };
             const bool last_chunk = rec[4] == NO_PART || rec[4] - rec[5] == rec[6] - 1;
@@ -354,7 +375,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 if (lane == 0 && !(last_chunk && a.k_new != nullptr)) {
                     const uint32_t pre = ntiles < SM::stages ? ntiles : SM::stages;
                     for (; tau0 < pre; tau0++)
-                        if (!issue_tile(tau0)) { failed = true; break; }
+                        if (!issue_tile()) { failed = true; break; }
                 }
                 grid_dep_wait();
             }
@@ -383,23 +404,46 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 }
                 __syncwarp();
             }
-            if (lane == 0) {
+            // The group's query rows, one copy each, issued side by side by the first lanes.
+            if (lane == 0) mbar_expect_tx(qfull0 + qslot * 8, nheads * D * 4);
+            __syncwarp();
+            if (lane < nheads) {
                 asm volatile("fence.proxy.async.global;" ::: "memory");
-                mbar_expect_tx(qfull0 + qslot * 8, nheads * D * 4);
-                const float* qp = a.q + ((size_t)seq * a.heads + head0) * D;
-                for (uint32_t h = 0; h < nheads; h++)
-                    bulk_g2s(sbase + SM::q_off + (qslot * 8 + h) * SM::q_stride, qp + (size_t)h * D, D * 4, qfull0 + qslot * 8);
-                // Item k + 1: its index has had a whole item's time to come back.
-                fetch(k + 1, idx_next);
-                if (!queue_dry) {
-                    queue_dry = idx_next >= a.n_items;
-                    if (!queue_dry) idx_next = gridDim.x + atomicAdd(a.queue, 1u);
-                }
+                bulk_g2s(sbase + SM::q_off + (qslot * 8 + lane) * SM::q_stride, a.q + ((size_t)seq * a.heads + head0 + lane) * D, D * 4,
+                         qfull0 + qslot * 8);
+            }
+            if (lane == 0) {
 #ifdef QVX_TRACE
                 TRACE(tp, 2);  // item issue begins
 #endif
-                for (uint32_t tau = tau0; tau < ntiles && !failed; tau++)
-                    if (!issue_tile(tau)) failed = true;
+                // Item k + 1 is claimed late: CLAIM_AHEAD tiles before this item's last tile is
+                // asked for, which is about the time its index and then its record take to come
+                // back.  A CTA so never sits on work that an idle CTA could take: the launch ends
+                // within a few tiles' time of the queue running dry.
+                uint32_t claim_at = ntiles > CLAIM_AHEAD ? ntiles - CLAIM_AHEAD : 0u;
+                uint32_t fetch_at = ntiles > FETCH_AHEAD ? ntiles - FETCH_AHEAD : 0u;
+                claim_at = claim_at < tau0 ? tau0 : claim_at;
+                fetch_at = fetch_at < claim_at ? claim_at : fetch_at;
+                // The queue's answer is not touched before `fetch_at`: an instruction that needs it
+                // would hold up the tiles issued in between for the atomic's round trip.
+                uint32_t claimed = 0;
+                bool asked = false, fetched = false;
+                auto fetch_next = [&]() {
+                    asm volatile("" : "+r"(claimed));  // nothing computed from the answer moves above this point
+                    const uint32_t idx_next = asked ? gridDim.x + claimed : a.n_items;
+                    fetch(k + 1, idx_next);
+                    queue_dry = idx_next >= a.n_items;
+                    fetched = true;
+                };
+                for (uint32_t tau = tau0; tau < ntiles && !failed; tau++) {
+                    if (tau == claim_at && !queue_dry) { claimed = atomicAdd(a.queue, 1u); asked = true; }
+                    if (tau == fetch_at) fetch_next();
+                    if (!issue_tile()) failed = true;
+                }
+                if (!fetched && !failed) {  // every tile went out before the dependency wait
+                    if (!queue_dry) { claimed = atomicAdd(a.queue, 1u); asked = true; }
+                    fetch_next();
+                }
 #ifdef QVX_TRACE
                 TRACE(tp, 3);  // item issue ends
 #endif
@@ -423,26 +467,78 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
 
     if (warp == CW + 1) {
         // ================================ epilogue ================================
-        // Takes the chunks whose partials the consumers have stored, one mail each, and does
-        // what would otherwise stall them: the device-wide fence, the arrival count and, for
-        // the last chunk of a sequence to arrive, the merge.
-        if (a.overlap) grid_dep_wait();
+        // The consumer warps never wait for one another: each leaves its state of an item (its
+        // maxima, row sums and unnormalised outputs over the tiles it took) in a buffer and goes
+        // on with the next item.  This warp puts the item together: it merges the CW states in
+        // the order of the tiles' places in the item, stores the chunk's partial result (or the
+        // output, for a sequence in one piece), gives the buffer back, and then does what has
+        // device-wide latency: the fence, the arrival count and, for the last chunk of a
+        // sequence to arrive, the merge over chunks.
+        if (a.overlap) grid_dep_wait();  // before this grid's first write to `out` or the scratch
+        constexpr uint32_t F4 = 8 * D / 4;
+        constexpr uint32_t PART_STRIDE = 8 * D + 16;
+        constexpr int NJ = F4 / 32;
+        const float* res_all = reinterpret_cast<const float*>(smem + SM::res_off);
 #ifdef QVX_TRACE
         const uint32_t trace_base = TRACE_PER_CTA / 4; uint32_t tp = 0;
 #endif
         for (uint32_t kp = 0;; kp++) {
             const uint32_t ms = kp % MAIL_SLOTS;
-            if (!__all_sync(0xffffffffu, mbar_wait(mfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;  // the abort path
+            if (!__all_sync(0xffffffffu, mbar_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;  // the abort path
             Mail m;
             m.seq = mailbox[ms].seq; m.head0 = mailbox[ms].head0; m.nheads = mailbox[ms].nheads; m.part0 = mailbox[ms].part0;
             m.nch = mailbox[ms].nch; m.counter = mailbox[ms].counter; m.stop = mailbox[ms].stop; m.chunk = mailbox[ms].chunk;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(mfree0 + ms * 8);
 #ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, m.stop ? 12 : 10);  // mail taken / stop
+            if (lane == 0) TRACE(tp, m.stop ? 12 : 10);  // item taken / stop
 #endif
             if (m.stop) return;
-            deliver<D>(a, m, m.chunk, lane);
+            const bool direct = m.chunk == NO_PART;
+            const float* rb = res_all + ms * CW * SM::res_floats;
+            float* pbase = direct ? nullptr : a.partials + (size_t)(m.part0 + m.chunk) * PART_STRIDE;
+            // Output i = lane + 32 j of the item's 8 x D/4 float4 values.
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const uint32_t i = lane + j * 32, h = i / (D / 4), x = (i % (D / 4)) * 4;
+                float M = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < CW; c++) M = fmaxf(M, rb[c * SM::res_floats + h]);
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float l = 0.f;
+#pragma unroll
+                for (int c = 0; c < CW; c++) {
+                    const float* r = rb + c * SM::res_floats;
+                    const float wg = ex2(r[h] - M);
+                    const float4 v = *reinterpret_cast<const float4*>(r + 16 + h * D + x);
+                    acc.x = fmaf(v.x, wg, acc.x); acc.y = fmaf(v.y, wg, acc.y);
+                    acc.z = fmaf(v.z, wg, acc.z); acc.w = fmaf(v.w, wg, acc.w);
+                    l = fmaf(r[8 + h], wg, l);
+                }
+                if (h < m.nheads) {
+                    if (direct)
+                        *reinterpret_cast<float4*>(a.out + ((size_t)m.seq * a.heads + m.head0 + h) * D + x) =
+                            make_float4(acc.x / l, acc.y / l, acc.z / l, acc.w / l);
+                    else
+                        *reinterpret_cast<float4*>(pbase + h * D + x) = acc;
+                }
+            }
+            if (!direct && lane < 8) {  // the chunk's maxima and row sums, once
+                float M = -INFINITY, l = 0.f;
+#pragma unroll
+                for (int c = 0; c < CW; c++) M = fmaxf(M, rb[c * SM::res_floats + lane]);
+#pragma unroll
+                for (int c = 0; c < CW; c++) {
+                    const float* r = rb + c * SM::res_floats;
+                    l = fmaf(r[8 + lane], ex2(r[lane] - M), l);
+                }
+                pbase[8 * D + lane] = M;
+                pbase[8 * D + 8 + lane] = l;
+            }
+            __syncwarp();  // every lane has read what it needs of the buffer
+            if (lane == 0) mbar_arrive(rfree0 + ms * 8);
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, 13);  // states merged, buffer given back
+#endif
+            if (!direct) deliver<D>(a, m, m.chunk, lane);
 #ifdef QVX_TRACE
             if (lane == 0) TRACE(tp, 11);  // deliver done
 #endif
@@ -454,20 +550,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     const uint32_t mid = lane >> 3, r8 = lane & 7;
     const uint32_t k_row = r8 + 8 * (mid & 1), k_chunk = mid >> 1;  // keys: A = K
     const uint32_t v_row = r8 + 8 * (mid >> 1), v_chunk = mid & 1;  // values: A = V^T (ldmatrix.trans)
-    const uint32_t tid_c = warp * 32 + lane;
-    constexpr uint32_t F4 = 8 * D / 4;                 // float4 values of one item's output
-    constexpr uint32_t PART_STRIDE = 8 * D + 16;  // floats per partial: acc[8][D], m[8], l[8]
     float* res_all = reinterpret_cast<float*>(smem + SM::res_off);
-    float* res = res_all + warp * SM::res_floats;
     uint32_t nbase = 0;   // tiles of the items before this one
-    uint32_t kp = 0;      // mails sent to the epilogue warp so far
 #ifdef QVX_TRACE
     const uint32_t trace_base = TRACE_PER_CTA / 2 + (warp == 0 ? 0 : TRACE_PER_CTA / 4); uint32_t tp = 0;
     const bool tr = lane == 0 && (warp == 0 || warp == CW - 1);
 #endif
-    bool dead = false;    // this warp gave up a wait: it only keeps the barriers company from here on
+    bool dead = false;    // this warp gave up a wait
     for (uint32_t k = 0;; k++) {
-        const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
+        const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS, ms = k % MAIL_SLOTS;
         Item it{};
         if (!dead && !__all_sync(0xffffffffu, mbar_wait(qfull0 + qslot * 8, (k / Q_SLOTS) & 1))) dead = true;
         // The record came by bulk copy: observe its own barrier too before reading it.
@@ -476,15 +567,30 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             const uint32_t* rec = reinterpret_cast<const uint32_t*>(smem + SM::rec_off) + rslot * REC_WORDS;
             it.seq = rec[0]; it.tokens = rec[1]; it.head0 = rec[2]; it.nheads = rec[3] & 0xffffu; it.kv_head = rec[3] >> 16;
             it.part = rec[4]; it.part0 = rec[5]; it.nch = rec[6]; it.counter = rec[7];
-            if (it.tokens == 0) break;  // the end of the queue: every consumer warp reads the same record
+        }
+        if (dead) {
+            // Every other wait in the CTA is bounded too: the others give up in their turn.
+            *abort_flag = 1;
+            if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+            return;
+        }
+        if (it.tokens == 0) {
+            // The end of the queue (every consumer warp reads the same record): tell the epilogue
+            // warp to leave once it has finished what it holds.
+            if (!__all_sync(0xffffffffu, mbar_wait(rfree0 + ms * 8, ((k / MAIL_SLOTS) & 1) ^ 1))) return;
+            if (warp == 0 && lane == 0) mailbox[ms].stop = 1;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(rfull0 + ms * 8);
+            return;
         }
 #ifdef QVX_TRACE
         if (tr) TRACE(tp, 20);  // item header read
 #endif
-        // The warp that takes the item's tiles 0, CW, 2 CW, ...: the merge below goes through the
-        // warps in the order of the tiles they took, so that the sum order does not depend on
-        // how many tiles this CTA happened to stream before the item.
-        const uint32_t rot = (CW - nbase % CW) % CW;
+        // Tiles are dealt to the warps by their number in the whole stream; this warp takes the
+        // item's tiles first, first + CW, ...  Its state goes to place `first` of the buffer, so
+        // the merge runs in the order of the tiles' places in the item and the sum order does not
+        // depend on how many tiles this CTA happened to stream before the item.
+        const uint32_t first = (warp + CW - nbase % CW) % CW;
         float o[D / 16][4];
 #pragma unroll
         for (int m = 0; m < D / 16; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; }
@@ -510,8 +616,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             if (lane == 0) mbar_arrive(qempty0 + qslot * 8);  // the producer may reuse this query slot
 
             const uint32_t ntiles = (it.tokens + TILE - 1) / TILE;
-            // Tiles are dealt to the warps by their number in the whole stream, not in the item.
-            for (uint32_t tau = (warp + CW - nbase % CW) % CW; tau < ntiles; tau += CW) {
+            for (uint32_t tau = first; tau < ntiles; tau += CW) {
                 const uint32_t n = nbase + tau;
                 const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
                 if (!__all_sync(0xffffffffu, mbar_wait(full0 + st * 8, ph))) { dead = true; break; }
@@ -590,11 +695,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         if (dead) {
             *abort_flag = 1;
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+            return;
         }
-        if (k == 0 && a.overlap) grid_dep_wait();  // before this grid's first write to `out` or the scratch
-        // ---- the consumers' states meet in shared memory --------------------------------------
-        consumer_barrier();  // the previous item's merge has read everything it needed
-        if (*abort_flag) return;  // uniform: every consumer warp sees the flag after the barrier
+        // ---- this warp's state goes to the epilogue warp, and the warp goes on -------------------
+        // The buffer is free once the epilogue warp has merged the item two before this one.
+        if (!__all_sync(0xffffffffu, mbar_wait(rfree0 + ms * 8, ((k / MAIL_SLOTS) & 1) ^ 1))) {
+            *abort_flag = 1;
+            if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+            return;
+        }
+        float* res = res_all + (ms * CW + first) * SM::res_floats;
         if (g == 0) {
             res[2 * t] = m0; res[2 * t + 1] = m1;
             res[8 + 2 * t] = l0; res[8 + 2 * t + 1] = l1;
@@ -606,81 +716,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             res[16 + (2 * t) * D + 16 * mt + g + 8] = o[mt][2];
             res[16 + (2 * t + 1) * D + 16 * mt + g + 8] = o[mt][3];
         }
-        consumer_barrier();
-#ifdef QVX_TRACE
-        if (tr) TRACE(tp, 22);  // both barriers passed
-#endif
-        // Each thread merges its share of the item's float4 outputs over the CW warps.
-        const bool direct = it.part == NO_PART;
-        float* pbase = direct ? nullptr : a.partials + (size_t)it.part * PART_STRIDE;
-#pragma unroll
-        for (uint32_t j = 0; j < (F4 + CT - 1) / CT; j++) {
-            const uint32_t i = tid_c + j * CT;
-            if (i >= F4) break;
-            const uint32_t h = i / (D / 4), x = (i % (D / 4)) * 4;
-            if (h >= it.nheads) continue;
-            float M = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < CW; w++) M = fmaxf(M, res_all[w * SM::res_floats + h]);
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float l = 0.f;
-#pragma unroll
-            for (int c = 0; c < CW; c++) {
-                const float* r = res_all + ((c + rot) % CW) * SM::res_floats;
-                const float wg = ex2(r[h] - M);
-                const float4 v = *reinterpret_cast<const float4*>(r + 16 + h * D + x);
-                acc.x = fmaf(v.x, wg, acc.x); acc.y = fmaf(v.y, wg, acc.y);
-                acc.z = fmaf(v.z, wg, acc.z); acc.w = fmaf(v.w, wg, acc.w);
-                l = fmaf(r[8 + h], wg, l);
-            }
-            if (direct) {
-                *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0 + h) * D + x) =
-                    make_float4(acc.x / l, acc.y / l, acc.z / l, acc.w / l);
-            } else {
-                *reinterpret_cast<float4*>(pbase + h * D + x) = acc;
-            }
-        }
-        if (direct) continue;
-        // The chunk's maxima and row sums, once.
-        if (warp == 0 && lane < 8) {
-            float M = -INFINITY, l = 0.f;
-#pragma unroll
-            for (int w = 0; w < CW; w++) M = fmaxf(M, res_all[w * SM::res_floats + lane]);
-#pragma unroll
-            for (int c = 0; c < CW; c++) {
-                const float* r = res_all + ((c + rot) % CW) * SM::res_floats;
-                l = fmaf(r[8 + lane], ex2(r[lane] - M), l);
-            }
-            pbase[8 * D + lane] = M;
-            pbase[8 * D + 8 + lane] = l;
-        }
-        // Hand the chunk to the epilogue warp and go on with the next item.
-        const uint32_t ms = kp % MAIL_SLOTS;
-        if (warp == 0) {
-            if (!__all_sync(0xffffffffu, mbar_wait(mfree0 + ms * 8, ((kp / MAIL_SLOTS) & 1) ^ 1))) {
-                *abort_flag = 1;  // seen by everyone at the next item's barrier
-            } else if (lane == 0) {
-                mailbox[ms].seq = it.seq; mailbox[ms].head0 = it.head0; mailbox[ms].nheads = it.nheads;
-                mailbox[ms].part0 = it.part0; mailbox[ms].nch = it.nch; mailbox[ms].counter = it.counter; mailbox[ms].stop = 0;
-                mailbox[ms].chunk = it.part - it.part0;
-            }
+        if (warp == 0 && lane == 0) {
+            mailbox[ms].seq = it.seq; mailbox[ms].head0 = it.head0; mailbox[ms].nheads = it.nheads;
+            mailbox[ms].part0 = it.part0; mailbox[ms].nch = it.nch; mailbox[ms].counter = it.counter; mailbox[ms].stop = 0;
+            mailbox[ms].chunk = it.part == NO_PART ? NO_PART : it.part - it.part0;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(mfull0 + ms * 8);
-        kp++;
+        if (lane == 0) mbar_arrive(rfull0 + ms * 8);
 #ifdef QVX_TRACE
-        if (tr) TRACE(tp, 23);  // mail sent
+        if (tr) TRACE(tp, 23);  // state handed over
 #endif
-    }
-    // The end of the queue: tell the epilogue warp to finish what it holds and leave.
-    {
-        const uint32_t ms = kp % MAIL_SLOTS;
-        if (warp == 0) {
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(mfree0 + ms * 8, ((kp / MAIL_SLOTS) & 1) ^ 1));
-            if (ok && lane == 0) mailbox[ms].stop = 1;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(mfull0 + ms * 8);
     }
 }
 

@@ -365,3 +365,26 @@ def test_more_ops_in_flight_than_the_staging_ring_holds(dev):
         assert np.array_equal(alone[0].view(np.uint32), first.view(np.uint32))
     finally:
         buf.free()
+
+
+def test_batch_invariance_when_ctas_stream_many_ragged_items(dev):
+    # More (sequence, group) pairs than resident CTAs, lengths that are no multiple of anything:
+    # every CTA streams several items, and most start at an arbitrary place of its tile stream.
+    # A sequence's bits must still equal those it gets alone (one item, first in its CTA's stream).
+    rng = np.random.default_rng(91)
+    lengths = [int(x) for x in rng.integers(1, 900, size=360)]
+    full = Case(32, 4, 128, 16, "bf16", lengths, seed=92, amp_qk=0.3)
+    _, out_full = full.run_device(dev, variant=qd.ATTN_SPLIT)
+    assert np.all(np.isfinite(out_full))
+    for t in (0, 7, 123, 359, int(np.argmax(full.lengths)), int(np.argmin(full.lengths))):
+        n = int(full.lengths[t])
+        alone = Case(32, 4, 128, 16, "bf16", [n], seed=93, pool_blocks=full.pool_blocks)
+        nb = (n + 15) // 16
+        alone.blocks = full.blocks[full.table_at[t]:full.table_at[t] + nb].copy()
+        alone.table_at[:] = 0
+        alone.q, alone.k_new, alone.v_new = full.q[t:t + 1], full.k_new[t:t + 1], full.v_new[t:t + 1]
+        lo = int(sum(int(x) - 1 for x in full.lengths[:t]))
+        alone.sync = full.sync[lo:lo + n - 1]
+        alone.sync_to = full.sync_to[lo:lo + n - 1]
+        _, out_alone = alone.run_device(dev, variant=qd.ATTN_SPLIT)
+        assert np.array_equal(out_alone[0].view(np.uint32), out_full[t].view(np.uint32)), t
