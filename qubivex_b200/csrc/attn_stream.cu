@@ -51,7 +51,8 @@ namespace qvx {
 constexpr int CW = QVX_CW;
 constexpr int CT = CW * 32;                    // consumer threads
 constexpr int STREAM_THREADS = CT + 64;        // + the producer warp and the epilogue warp
-constexpr int MAIL_SLOTS = 2;                  // one per buffer of consumer states
+constexpr int MAIL_SLOTS = 2;                  // buffers of consumer states: one being merged, one being filled
+constexpr int NOTE_SLOTS = 4;                  // items the epilogue warp is told about ahead of their states
 constexpr int Q_SLOTS = 2;
 constexpr int REC_SLOTS = 4;
 #ifndef QVX_CLAIM_AHEAD
@@ -128,16 +129,17 @@ struct StreamSmem {
     static constexpr uint32_t rec_off = q_off + q_bytes;
     static constexpr uint32_t bar_off = rec_off + rec_bytes;
     // full[stages], empty[stages], qfull[Q_SLOTS], qempty[Q_SLOTS], rec[REC_SLOTS],
-    // res_full[MAIL_SLOTS], res_free[MAIL_SLOTS], then the abort word and the mailbox
-    static constexpr uint32_t n_bars = 2 * stages + 2 * Q_SLOTS + REC_SLOTS + 2 * MAIL_SLOTS;
+    // res_full[MAIL_SLOTS], res_free[MAIL_SLOTS], note[NOTE_SLOTS], then the abort word and the notes
+    static constexpr uint32_t n_bars = 2 * stages + 2 * Q_SLOTS + REC_SLOTS + 2 * MAIL_SLOTS + NOTE_SLOTS;
     static constexpr uint32_t abort_off = bar_off + n_bars * 8;
     static constexpr uint32_t mail_off = abort_off + 16;
-    static constexpr uint32_t total = mail_off + MAIL_SLOTS * 32;
+    static constexpr uint32_t total = mail_off + NOTE_SLOTS * 32;
     static_assert(stages >= CW, "the ring needs a stage per consumer warp");
 };
 
-// What the consumers tell the epilogue warp about the item whose states they have left in a buffer.
-// `chunk` is the item's place among its sequence's chunks, NO_PART for a sequence in one piece.
+// What the consumers tell the epilogue warp about an item when they start it, long before its
+// states are ready.  `chunk` is the item's place among its sequence's chunks, NO_PART for a
+// sequence in one piece; `stop` marks the end of the queue.
 struct Mail {
     uint32_t seq, head0, nheads, part0, nch, counter, stop, chunk;
 };
@@ -159,110 +161,212 @@ __host__ __device__ inline uint32_t merge_entries_total(uint32_t nch) {
     while (n > MERGE_FAN) { n = (n + MERGE_FAN - 1) / MERGE_FAN; total += n; }
     return total;
 }
+// Two words per node: arrivals claimed, entries published.
 __host__ __device__ inline uint32_t merge_counters_total(uint32_t nch) {
     uint32_t total = 0, n = nch;
     for (;;) {
-        total += (n + MERGE_FAN - 1) / MERGE_FAN;
+        total += 2 * ((n + MERGE_FAN - 1) / MERGE_FAN);
         if (n <= MERGE_FAN) break;
         n = (n + MERGE_FAN - 1) / MERGE_FAN;
     }
     return total;
 }
 
-// Run by the epilogue warp for one chunk whose partial the consumers have stored: counts the
-// arrival and climbs the tree as far as this arrival completes nodes.
+// Run by the epilogue warp with a chunk's merged result in registers (output i = lane + 32 j of
+// the chunk's 8 x D/4 float4 values in E[j], the maximum and row sum of that output's head in
+// Em[j], El[j]).  It counts the arrival at the chunk's node and climbs the tree as far as this
+// arrival completes nodes.
+//
+// A node has two words.  An arrival first takes a number from `claimed`.  Every arrival but the
+// last stores its entry, fences, and adds one to `published`: nothing waits for that.  The last
+// arrival keeps its entry in registers, waits (bounded) until `published` shows the others, and
+// merges the node: the others' entries from memory, its own from registers, in entry order.  So
+// the chunk that finishes a sequence pays one atomic round trip and the loads, not a store, a
+// fence, an atomic and the loads.  The merge keeps a running maximum, so an entry's maximum is
+// needed only together with its values: no round of loads for the maxima first.
+// A running merge over entries of a node: unnormalised outputs, running maxima and row sums
+// (output i = lane + 32 j of the 8 x D/4 float4 values; the maximum and sum of that output's head).
 template <int D>
-__device__ __forceinline__ void deliver(const StreamArgs& a, const Mail& it, uint32_t chunk, uint32_t lane) {
-    constexpr uint32_t F4 = 8 * D / 4;
+struct Running {
+    static constexpr int NJ = 8 * D / 4 / 32;
+    float4 acc[NJ];
+    float M[NJ], L[NJ];
+    __device__ __forceinline__ void clear() {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) { acc[j] = make_float4(0.f, 0.f, 0.f, 0.f); M[j] = -INFINITY; L[j] = 0.f; }
+    }
+};
+
+// Folds entries c0 .. c1-1 of the node whose first entry is at p0 into `r`, in entry order.  Entry
+// `mine` is not read from memory: it is E (values) and Eml (lane h < 8: maximum of head h, lane
+// 8 + h: its row sum).  PAIR entries' loads are in flight at a time.
+template <int D, int PAIR>
+__device__ __forceinline__ void fold_range(Running<D>& r, const float* p0, uint32_t c0, uint32_t c1, uint32_t mine,
+                                           const float4 (&E)[8 * D / 4 / 32], float Eml, uint32_t lane) {
     constexpr uint32_t PART_STRIDE = 8 * D + 16;
-    constexpr int NJ = F4 / 32;
-    const uint32_t hl = lane & 7;
-    uint32_t n = it.nch, idx = chunk, part_base = it.part0, cnt_base = it.counter;
+    constexpr int NJ = 8 * D / 4 / 32;
+    for (uint32_t c = c0; c < c1; c += PAIR) {
+        float4 v[PAIR][NJ];
+        float ml[PAIR];
+#pragma unroll
+        for (int u = 0; u < PAIR; u++) {
+            const float* pe = p0 + (size_t)(c + u) * PART_STRIDE;
+            const bool load = c + u < c1 && c + u != mine;
+            ml[u] = Eml;
+            if (load && lane < 16) ml[u] = __ldcg(pe + 8 * D + lane);
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const uint32_t i = lane + j * 32, h = i / (D / 4);
+                v[u][j] = load ? __ldcg(reinterpret_cast<const float4*>(pe + h * D + (i % (D / 4)) * 4)) : E[j];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PAIR; u++) {
+            if (c + u >= c1) break;
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const uint32_t h = (lane + j * 32) / (D / 4);
+                const float m = __shfl_sync(0xffffffffu, ml[u], h), l = __shfl_sync(0xffffffffu, ml[u], 8 + h);
+                const float mn = fmaxf(r.M[j], m);
+                const float so = ex2(r.M[j] - mn), w = ex2(m - mn);
+                r.acc[j].x = fmaf(v[u][j].x, w, r.acc[j].x * so); r.acc[j].y = fmaf(v[u][j].y, w, r.acc[j].y * so);
+                r.acc[j].z = fmaf(v[u][j].z, w, r.acc[j].z * so); r.acc[j].w = fmaf(v[u][j].w, w, r.acc[j].w * so);
+                r.L[j] = fmaf(l, w, r.L[j] * so);
+                r.M[j] = mn;
+            }
+        }
+    }
+}
+
+// Release / acquire fences at device scope (__threadfence() is the sequentially consistent one).
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
+// Waits (bounded) until a node's `published` word shows `want` entries.
+__device__ __forceinline__ bool wait_published(const uint32_t* published, uint32_t want) {
+    bool seen = false;
+    for (uint32_t i = 0; i < WAIT_LIMIT && !seen; i++) {
+        seen = *reinterpret_cast<const volatile uint32_t*>(published) == want;
+        if (!seen && i > 64) __nanosleep(32);
+    }
+    return __all_sync(0xffffffffu, seen);
+}
+
+// Run by the epilogue warp when it learns of a split item, while the consumers are still
+// streaming it.  If every other chunk of the item's node has already arrived, this item is the
+// node's last arrival for certain, and the entries before it can be folded now: when the item's
+// own result is ready only that (and the entries after it, if any) remain.  Returns whether
+// `r` holds that prefix.
+template <int D>
+__device__ __forceinline__ bool fold_ahead(const StreamArgs& a, const Mail& it, uint32_t lane, Running<D>& r) {
+    constexpr uint32_t PART_STRIDE = 8 * D + 16;
+    const uint32_t node = it.chunk / MERGE_FAN, first = node * MERGE_FAN, size = min(MERGE_FAN, it.nch - first), mine = it.chunk - first;
+    if (size < 2) return false;
+    const uint32_t* claimed = a.counters + it.counter + 2 * node;
+    uint32_t others = 0;
+    if (lane == 0) others = *reinterpret_cast<const volatile uint32_t*>(claimed);
+    if (__shfl_sync(0xffffffffu, others, 0) != size - 1) return false;
+    if (!wait_published(claimed + 1, size - 1)) return false;  // the caller's own wait reports a failure
+    fence_acq_rel_gpu();
+    r.clear();
+    float4 none[8 * D / 4 / 32];
+#pragma unroll
+    for (int j = 0; j < 8 * D / 4 / 32; j++) none[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    fold_range<D, (8 * D / 4 / 32 <= 8 ? 3 : 1)>(r, a.partials + (size_t)(it.part0 + first) * PART_STRIDE, 0, mine, NO_PART, none, 0.f, lane);
+    return true;
+}
+
+// Run by the epilogue warp with a chunk's merged result in registers (E, Eml as in fold_range).
+// It counts the arrival at the chunk's node and climbs the tree as far as this arrival completes
+// nodes.
+//
+// A node has two words.  An arrival first takes a number from `claimed`.  Every arrival but the
+// last stores its entry, fences, and adds one to `published`: nothing waits for that.  The last
+// arrival keeps its entry in registers, waits (bounded) until `published` shows the others, and
+// merges the node: the others' entries from memory, its own from registers, in entry order.  So
+// the chunk that finishes a sequence pays one atomic round trip and the loads, not a store, a
+// fence, an atomic and the loads -- and with `ahead` (fold_ahead succeeded) not even those.  The
+// merge keeps a running maximum, so an entry's maximum is needed only together with its values.
+template <int D>
+__device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint32_t lane, float4 (&E)[8 * D / 4 / 32], float Eml,
+                                      bool ahead, Running<D>& r
+#ifdef QVX_TRACE
+                                      , uint32_t& tp, const uint32_t trace_base
+#endif
+) {
+    constexpr uint32_t PART_STRIDE = 8 * D + 16;
+    constexpr int NJ = 8 * D / 4 / 32;
+    uint32_t hh[NJ], off[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        const uint32_t i = lane + j * 32;
+        hh[j] = i / (D / 4);
+        off[j] = hh[j] * D + (i % (D / 4)) * 4;
+    }
+    uint32_t n = it.nch, idx = it.chunk, part_base = it.part0, cnt_base = it.counter;
     for (;;) {
-        const uint32_t node = idx / MERGE_FAN, first = node * MERGE_FAN, size = min(MERGE_FAN, n - first);
-        __threadfence();  // what this entry holds (seen through the mailbox barrier, or written just above) is visible first
-        __syncwarp();
-        uint32_t last = 0;
-        if (lane == 0) last = atomicAdd(a.counters + cnt_base + node, 1u) == size - 1 ? 1u : 0u;
-        if (!__shfl_sync(0xffffffffu, last, 0)) return;
-        __threadfence();
-        if (lane == 0) a.counters[cnt_base + node] = 0;  // ready for the next launch
-        const float* p0 = a.partials + (size_t)(part_base + first) * PART_STRIDE;
-        const float* ml = p0 + 8 * D;
-        // Maxima and row sums of the node's entries: lane = (entry, head), one round of loads.
-        float M = -INFINITY, L = 0.f;
-        {
-            float mv[MERGE_FAN / 4 > 0 ? (MERGE_FAN + 3) / 4 : 1], lv[(MERGE_FAN + 3) / 4];
+        const uint32_t node = idx / MERGE_FAN, first = node * MERGE_FAN, size = min(MERGE_FAN, n - first), mine = idx - first;
+        uint32_t* claimed = a.counters + cnt_base + 2 * node;
+        uint32_t* published = claimed + 1;
+        float* p0 = a.partials + (size_t)(part_base + first) * PART_STRIDE;
+        if (!ahead) {
+            uint32_t last = 0;
+            if (lane == 0) last = atomicAdd(claimed, 1u) == size - 1 ? 1u : 0u;
+            last = __shfl_sync(0xffffffffu, last, 0);
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, last ? 14 : 17);  // claim answered
+#endif
+            if (!last) {
+                float* pe = p0 + (size_t)mine * PART_STRIDE;
 #pragma unroll
-            for (int u = 0; u < (int)((MERGE_FAN + 3) / 4); u++) {
-                const uint32_t c = (lane >> 3) + 4 * u;
-                mv[u] = c < size ? __ldcg(ml + (size_t)c * PART_STRIDE + hl) : -INFINITY;
-                lv[u] = c < size ? __ldcg(ml + (size_t)c * PART_STRIDE + 8 + hl) : 0.f;
+                for (int j = 0; j < NJ; j++) *reinterpret_cast<float4*>(pe + off[j]) = E[j];
+                if (lane < 16) pe[8 * D + lane] = Eml;
+                fence_acq_rel_gpu();
+                __syncwarp();
+                if (lane == 0) atomicAdd(published, 1u);
+                return;
             }
-#pragma unroll
-            for (int u = 0; u < (int)((MERGE_FAN + 3) / 4); u++) M = fmaxf(M, mv[u]);
-            M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 8));
-            M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, 16));
-#pragma unroll
-            for (int u = 0; u < (int)((MERGE_FAN + 3) / 4); u++) L = fmaf(lv[u], ex2(mv[u] - M), L);
-            L += __shfl_xor_sync(0xffffffffu, L, 8);
-            L += __shfl_xor_sync(0xffffffffu, L, 16);
-        }
-        // Output i = lane + 32 j of the 8 x D/4 float4 values; all of a lane's outputs advance
-        // together, two entries at a time: 2 * NJ 16-byte loads in flight per lane.
-        float4 acc[NJ];
-        float Mh[NJ], Lh[NJ];
-        uint32_t off[NJ];
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-            const uint32_t i = lane + j * 32, hh = i / (D / 4);
-            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-            Mh[j] = __shfl_sync(0xffffffffu, M, hh);
-            Lh[j] = __shfl_sync(0xffffffffu, L, hh);
-            off[j] = hh * D + (i % (D / 4)) * 4;
-        }
-        for (uint32_t c = 0; c < size; c += 2) {
-            const bool two = c + 1 < size;
-            const float* pa = p0 + (size_t)c * PART_STRIDE;
-            const float* pb = two ? pa + PART_STRIDE : pa;
-            float4 va[NJ], vb[NJ];
-            float wa[NJ], wb[NJ];
-#pragma unroll
-            for (int j = 0; j < NJ; j++) {
-                const uint32_t hh = (lane + j * 32) / (D / 4);
-                va[j] = __ldcg(reinterpret_cast<const float4*>(pa + off[j]));
-                vb[j] = __ldcg(reinterpret_cast<const float4*>(pb + off[j]));
-                wa[j] = __ldcg(pa + 8 * D + hh);
-                wb[j] = __ldcg(pb + 8 * D + hh);
+            // The last arrival: the others have claimed before it, and publish within a store and a fence.
+            if (!wait_published(published, size - 1)) {
+                if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+                return;
             }
-#pragma unroll
-            for (int j = 0; j < NJ; j++) {
-                const float ga = ex2(wa[j] - Mh[j]), gb = two ? ex2(wb[j] - Mh[j]) : 0.f;
-                acc[j].x = fmaf(va[j].x, ga, acc[j].x); acc[j].y = fmaf(va[j].y, ga, acc[j].y);
-                acc[j].z = fmaf(va[j].z, ga, acc[j].z); acc[j].w = fmaf(va[j].w, ga, acc[j].w);
-                acc[j].x = fmaf(vb[j].x, gb, acc[j].x); acc[j].y = fmaf(vb[j].y, gb, acc[j].y);
-                acc[j].z = fmaf(vb[j].z, gb, acc[j].z); acc[j].w = fmaf(vb[j].w, gb, acc[j].w);
-            }
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, 15);  // the others' entries are published
+#endif
+            fence_acq_rel_gpu();
+            r.clear();
         }
+        if (lane == 0) { *claimed = 0; *published = 0; }  // ready for the next launch
+        fold_range<D, (NJ <= 8 ? 2 : 1)>(r, p0, ahead ? mine : 0u, size, mine, E, Eml, lane);
+        ahead = false;
+#ifdef QVX_TRACE
+        if (lane == 0) TRACE(tp, 16);  // node merged
+#endif
         if (n <= MERGE_FAN) {
             // The root: the sequence's output.
 #pragma unroll
-            for (int j = 0; j < NJ; j++) {
-                const uint32_t hh = (lane + j * 32) / (D / 4);
-                if (hh < it.nheads)
+            for (int j = 0; j < NJ; j++)
+                if (hh[j] < it.nheads) {
+                    const float inv = 1.0f / r.L[j];
                     *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0) * D + off[j]) =
-                        make_float4(acc[j].x / Lh[j], acc[j].y / Lh[j], acc[j].z / Lh[j], acc[j].w / Lh[j]);
-            }
+                        make_float4(r.acc[j].x * inv, r.acc[j].y * inv, r.acc[j].z * inv, r.acc[j].w * inv);
+                }
             return;
         }
-        // An entry of the next level, in the same form as a chunk's partial.
-        const uint32_t next_base = part_base + n;
-        float* pn = a.partials + (size_t)(next_base + node) * PART_STRIDE;
+        // The node's result is this warp's entry of the next level.
 #pragma unroll
-        for (int j = 0; j < NJ; j++) *reinterpret_cast<float4*>(pn + off[j]) = acc[j];
-        if (lane < 8) { pn[8 * D + lane] = M; pn[8 * D + 8 + lane] = L; }
-        cnt_base += (n + MERGE_FAN - 1) / MERGE_FAN;
-        part_base = next_base;
+        for (int j = 0; j < NJ; j++) E[j] = r.acc[j];
+#pragma unroll
+        for (int h = 0; h < 8; h++) {
+            // Head h's first output, h * D/4, is held by lane (h * D/4) % 32 at j = (h * D/4) / 32.
+            constexpr int Q = D / 4;
+            const float mv = __shfl_sync(0xffffffffu, r.M[(h * Q) / 32], (h * Q) % 32);
+            const float lv = __shfl_sync(0xffffffffu, r.L[(h * Q) / 32], (h * Q) % 32);
+            if (lane == (uint32_t)h) Eml = mv;
+            if (lane == (uint32_t)(8 + h)) Eml = lv;
+        }
+        cnt_base += 2 * ((n + MERGE_FAN - 1) / MERGE_FAN);
+        part_base += n;
         n = (n + MERGE_FAN - 1) / MERGE_FAN;
         idx = node;
     }
@@ -276,7 +380,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     const uint32_t sbase = smem_u32(smem);
     const uint32_t full0 = sbase + SM::bar_off, empty0 = full0 + SM::stages * 8;
     const uint32_t qfull0 = empty0 + SM::stages * 8, qempty0 = qfull0 + Q_SLOTS * 8, recbar0 = qempty0 + Q_SLOTS * 8;
-    const uint32_t rfull0 = recbar0 + REC_SLOTS * 8, rfree0 = rfull0 + MAIL_SLOTS * 8;
+    const uint32_t rfull0 = recbar0 + REC_SLOTS * 8, rfree0 = rfull0 + MAIL_SLOTS * 8, note0 = rfree0 + MAIL_SLOTS * 8;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + SM::abort_off);
     volatile Mail* mailbox = reinterpret_cast<volatile Mail*>(smem + SM::mail_off);
 
@@ -290,6 +394,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         for (uint32_t s = 0; s < Q_SLOTS; s++) { mbar_init(qfull0 + s * 8, 1); mbar_init(qempty0 + s * 8, CW); }
         for (uint32_t s = 0; s < REC_SLOTS; s++) mbar_init(recbar0 + s * 8, 1);
         for (uint32_t s = 0; s < MAIL_SLOTS; s++) { mbar_init(rfull0 + s * 8, CW); mbar_init(rfree0 + s * 8, 1); }
+        for (uint32_t s = 0; s < NOTE_SLOTS; s++) mbar_init(note0 + s * 8, 1);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -475,70 +580,91 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         // device-wide latency: the fence, the arrival count and, for the last chunk of a
         // sequence to arrive, the merge over chunks.
         if (a.overlap) grid_dep_wait();  // before this grid's first write to `out` or the scratch
-        constexpr uint32_t F4 = 8 * D / 4;
-        constexpr uint32_t PART_STRIDE = 8 * D + 16;
-        constexpr int NJ = F4 / 32;
+        constexpr int NJ = 8 * D / 4 / 32;
         const float* res_all = reinterpret_cast<const float*>(smem + SM::res_off);
 #ifdef QVX_TRACE
         const uint32_t trace_base = TRACE_PER_CTA / 4; uint32_t tp = 0;
 #endif
+        Running<D> run;
         for (uint32_t kp = 0;; kp++) {
-            const uint32_t ms = kp % MAIL_SLOTS;
-            if (!__all_sync(0xffffffffu, mbar_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;  // the abort path
+            const uint32_t ms = kp % MAIL_SLOTS, ns = kp % NOTE_SLOTS;
+            // What the item is: the consumers say so when they start it.
+            if (!__all_sync(0xffffffffu, mbar_wait(note0 + ns * 8, (kp / NOTE_SLOTS) & 1))) return;  // the abort path
             Mail m;
-            m.seq = mailbox[ms].seq; m.head0 = mailbox[ms].head0; m.nheads = mailbox[ms].nheads; m.part0 = mailbox[ms].part0;
-            m.nch = mailbox[ms].nch; m.counter = mailbox[ms].counter; m.stop = mailbox[ms].stop; m.chunk = mailbox[ms].chunk;
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, m.stop ? 12 : 10);  // item taken / stop
-#endif
+            m.seq = mailbox[ns].seq; m.head0 = mailbox[ns].head0; m.nheads = mailbox[ns].nheads; m.part0 = mailbox[ns].part0;
+            m.nch = mailbox[ns].nch; m.counter = mailbox[ns].counter; m.stop = mailbox[ns].stop; m.chunk = mailbox[ns].chunk;
             if (m.stop) return;
+            // While they stream it: if the item is its node's last arrival, fold what precedes it.
+            const bool ahead = m.chunk != NO_PART && fold_ahead<D>(a, m, lane, run);
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, ahead ? 18 : 19);  // note read (and the node's other entries folded)
+#endif
+            if (!__all_sync(0xffffffffu, mbar_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;
+#ifdef QVX_TRACE
+            if (lane == 0) TRACE(tp, 10);  // states ready
+#endif
             const bool direct = m.chunk == NO_PART;
             const float* rb = res_all + ms * CW * SM::res_floats;
-            float* pbase = direct ? nullptr : a.partials + (size_t)(m.part0 + m.chunk) * PART_STRIDE;
-            // Output i = lane + 32 j of the item's 8 x D/4 float4 values.
+            // Output i = lane + 32 j of the item's 8 x D/4 float4 values, over the CW states in
+            // the order of the tiles' places in the item.
+            float4 E[NJ];
+            float El[NJ];
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
                 const uint32_t i = lane + j * 32, h = i / (D / 4), x = (i % (D / 4)) * 4;
+                float mc[CW];
                 float M = -INFINITY;
 #pragma unroll
-                for (int c = 0; c < CW; c++) M = fmaxf(M, rb[c * SM::res_floats + h]);
+                for (int c = 0; c < CW; c++) { mc[c] = rb[c * SM::res_floats + h]; M = fmaxf(M, mc[c]); }
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                 float l = 0.f;
 #pragma unroll
                 for (int c = 0; c < CW; c++) {
                     const float* r = rb + c * SM::res_floats;
-                    const float wg = ex2(r[h] - M);
+                    const float wg = ex2(mc[c] - M);
                     const float4 v = *reinterpret_cast<const float4*>(r + 16 + h * D + x);
                     acc.x = fmaf(v.x, wg, acc.x); acc.y = fmaf(v.y, wg, acc.y);
                     acc.z = fmaf(v.z, wg, acc.z); acc.w = fmaf(v.w, wg, acc.w);
                     l = fmaf(r[8 + h], wg, l);
                 }
-                if (h < m.nheads) {
-                    if (direct)
-                        *reinterpret_cast<float4*>(a.out + ((size_t)m.seq * a.heads + m.head0 + h) * D + x) =
-                            make_float4(acc.x / l, acc.y / l, acc.z / l, acc.w / l);
-                    else
-                        *reinterpret_cast<float4*>(pbase + h * D + x) = acc;
-                }
+                E[j] = acc; El[j] = l;
             }
-            if (!direct && lane < 8) {  // the chunk's maxima and row sums, once
+            // The chunk's maxima (lanes 0..7) and row sums (lanes 8..15), by the same sums.
+            float Eml = 0.f;
+            if (!direct) {
+                const uint32_t h = lane & 7;
                 float M = -INFINITY, l = 0.f;
 #pragma unroll
-                for (int c = 0; c < CW; c++) M = fmaxf(M, rb[c * SM::res_floats + lane]);
+                for (int c = 0; c < CW; c++) M = fmaxf(M, rb[c * SM::res_floats + h]);
 #pragma unroll
                 for (int c = 0; c < CW; c++) {
                     const float* r = rb + c * SM::res_floats;
-                    l = fmaf(r[8 + lane], ex2(r[lane] - M), l);
+                    l = fmaf(r[8 + h], ex2(r[h] - M), l);
                 }
-                pbase[8 * D + lane] = M;
-                pbase[8 * D + 8 + lane] = l;
+                Eml = lane < 8 ? M : l;
             }
             __syncwarp();  // every lane has read what it needs of the buffer
             if (lane == 0) mbar_arrive(rfree0 + ms * 8);
 #ifdef QVX_TRACE
             if (lane == 0) TRACE(tp, 13);  // states merged, buffer given back
 #endif
-            if (!direct) deliver<D>(a, m, m.chunk, lane);
+            if (direct) {
+#pragma unroll
+                for (int j = 0; j < NJ; j++) {
+                    const uint32_t i = lane + j * 32, h = i / (D / 4), x = (i % (D / 4)) * 4;
+                    if (h < m.nheads) {
+                        const float inv = 1.0f / El[j];
+                        *reinterpret_cast<float4*>(a.out + ((size_t)m.seq * a.heads + m.head0 + h) * D + x) =
+                            make_float4(E[j].x * inv, E[j].y * inv, E[j].z * inv, E[j].w * inv);
+                    }
+                }
+            } else {
+#ifdef QVX_TRACE
+                climb<D>(a, m, lane, E, Eml, ahead, run, tp, trace_base);
+#else
+                climb<D>(a, m, lane, E, Eml, ahead, run);
+#endif
+            }
 #ifdef QVX_TRACE
             if (lane == 0) TRACE(tp, 11);  // deliver done
 #endif
@@ -574,15 +700,18 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
         }
-        if (it.tokens == 0) {
-            // The end of the queue (every consumer warp reads the same record): tell the epilogue
-            // warp to leave once it has finished what it holds.
-            if (!__all_sync(0xffffffffu, mbar_wait(rfree0 + ms * 8, ((k / MAIL_SLOTS) & 1) ^ 1))) return;
-            if (warp == 0 && lane == 0) mailbox[ms].stop = 1;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(rfull0 + ms * 8);
-            return;
+        // The epilogue warp learns of the item now (or of the end of the queue).  It has finished
+        // item k - 3 at least -- the state buffers are handed over two at a time -- so note slot
+        // k % NOTE_SLOTS is free.
+        if (warp == 0 && lane == 0) {
+            const uint32_t ns = k % NOTE_SLOTS;
+            mailbox[ns].seq = it.seq; mailbox[ns].head0 = it.head0; mailbox[ns].nheads = it.nheads;
+            mailbox[ns].part0 = it.part0; mailbox[ns].nch = it.nch; mailbox[ns].counter = it.counter;
+            mailbox[ns].stop = it.tokens == 0 ? 1u : 0u;
+            mailbox[ns].chunk = it.part == NO_PART ? NO_PART : it.part - it.part0;
+            mbar_arrive(note0 + ns * 8);
         }
+        if (it.tokens == 0) return;  // the end of the queue: every consumer warp reads the same record
 #ifdef QVX_TRACE
         if (tr) TRACE(tp, 20);  // item header read
 #endif
@@ -715,11 +844,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             res[16 + (2 * t + 1) * D + 16 * mt + g] = o[mt][1];
             res[16 + (2 * t) * D + 16 * mt + g + 8] = o[mt][2];
             res[16 + (2 * t + 1) * D + 16 * mt + g + 8] = o[mt][3];
-        }
-        if (warp == 0 && lane == 0) {
-            mailbox[ms].seq = it.seq; mailbox[ms].head0 = it.head0; mailbox[ms].nheads = it.nheads;
-            mailbox[ms].part0 = it.part0; mailbox[ms].nch = it.nch; mailbox[ms].counter = it.counter; mailbox[ms].stop = 0;
-            mailbox[ms].chunk = it.part == NO_PART ? NO_PART : it.part - it.part0;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(rfull0 + ms * 8);
