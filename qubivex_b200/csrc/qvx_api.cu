@@ -257,10 +257,20 @@ static uint32_t chunk_tokens_for(const Layout& L, uint32_t len) {
         long n = v ? atol(v) : 0;
         return (uint32_t)(n > 0 ? n : 0);
     }();
-    uint32_t c = std::max(configured ? configured : 512u, L.B) / L.B * L.B;
+    static const uint32_t base = [] {  // experiments: the size the doubling starts from
+        const char* v = getenv("QVX_CHUNK_BASE");
+        long n = v ? atol(v) : 0;
+        return (uint32_t)(n > 0 ? n : 512);
+    }();
+    uint32_t c = std::max(configured ? configured : base, L.B) / L.B * L.B;
     while (c > 2048 && c > L.B) c -= L.B;
+    static const uint32_t most = [] {  // experiments: the chunk count beyond which the size doubles
+        const char* v = getenv("QVX_CHUNK_MOST");
+        long n = v ? atol(v) : 0;
+        return (uint32_t)(n > 0 ? n : 32);
+    }();
     if (!configured)
-        while ((len + c - 1) / c > 32 && c * 2 <= 2048) c *= 2;
+        while ((len + c - 1) / c > most && c * 2 <= 2048) c *= 2;
     return c;
 }
 
