@@ -118,7 +118,7 @@ int32_t qvx_get_transfers(qvx_device *dev, qvx_transfer_stats *out);
 #define QVX_K_SYNC 0
 #define QVX_K_APPEND 1
 #define QVX_K_ATTN 2     /* the split decode-attention kernel                              */
-#define QVX_K_REDUCE 3   /* unused: the split kernel merges its own partial results         */
+#define QVX_K_PRELUDE 3  /* clip, Q/K norms and RoPE before the store and attention            */
 #define QVX_K_EXACT 4    /* the reference-order decode-attention kernel                    */
 #define QVX_K_COPY 5     /* block copies (copy-on-write, compaction)                       */
 #define QVX_K_COUNT 6
@@ -206,6 +206,28 @@ int32_t qvx_attn_decode_static(qvx_device *dev, const qvx_geometry *geo, const v
                                size_t s, const float *q, const uint32_t *pos, const uint32_t *blocks,
                                const uint32_t *table_at, uint32_t max_pos, float *out, void *stream);
 
+/* The attention prelude: what SimDevice::attention does between the projections and the store
+ * (crates/qubivex-backend-cpu/src/sim.rs:333-357; the device statement is
+ * crates/qubivex-backend-vulkan/shaders/attn_prelude.comp:1-176), with the reference's bits:
+ * z.clamp(-clip, clip) on q, k and v; the full-width RMS norms of each token's q row
+ * (heads * head_dim values, weights q_norm) and k row (kv_heads * head_dim, k_norm) with the
+ * 64-lane sum of squares (crates/qubivex-compute/src/math.rs:88-117, reduce.rs:12-47); NeoX RoPE
+ * on every head of q and k from the token's table row [cos.., sin..] (math.rs:159-168).
+ * Mirrors DeviceMoeAttention's clip / qk_norm / eps / rope fields (discrete.rs:281-289). */
+typedef struct qvx_prelude {
+    uint32_t has_clip;    /* Option<f32>: 0 = None                                          */
+    float clip;           /* >= 0                                                           */
+    const float *q_norm;  /* Option<(&[f32], &[f32])>: both NULL, or heads * head_dim and   */
+    const float *k_norm;  /* kv_heads * head_dim weights                                    */
+    double eps;           /* narrowed to f32 before use, as the reference does              */
+    const float *rope;    /* s x head_dim, one row per token                                */
+} qvx_prelude;
+/* Device pointers throughout (the struct itself is read on the host); q [s][heads][d], k_new and
+ * v_new [s][kv_heads][d] are changed in place: afterwards they are what attention and the store
+ * take, and k_new / v_new what the host cache keeps (attn_prelude.comp's binding 2). */
+int32_t qvx_attn_prelude(qvx_device *dev, const qvx_geometry *geo, size_t heads, size_t s, float *q,
+                         float *k_new, float *v_new, const qvx_prelude *prelude, void *stream);
+
 /* Whole-block copies src[i] -> dst[i]: the copy of a shared block before the first
  * divergent append, and the moves of a compaction pass.  No counterpart in the reference,
  * which copies a whole cache (crates/qubivex-arch/src/lib.rs:409-432) and never moves a
@@ -239,6 +261,19 @@ int32_t qvx_paged_attention_host_async(qvx_device *dev, qvx_buffer *pool, const 
                                        const float *sync_host, const uint32_t *sync_to_host,
                                        size_t n_sync, float *out_host, uint32_t variant);
 int32_t qvx_wait(qvx_device *dev);
+
+/* DeviceMoeAttention after the projections only: the prelude above on the host's q, k_new and
+ * v_new (the raw projections; `prelude` holds host pointers here), then the op of
+ * qvx_paged_attention_host.  k_new_host and v_new_host are written back (clipped, normed,
+ * rotated), as SimDevice::attention leaves them for the host cache (sim.rs:325-357).
+ * Synchronous.  QVX_ERR_SHAPE (also for a negative or NaN clip) before anything is written. */
+int32_t qvx_attention_stage_host(qvx_device *dev, qvx_buffer *pool, const qvx_geometry *geo,
+                                 size_t heads, size_t s, const float *q_host, float *k_new_host,
+                                 float *v_new_host, const qvx_prelude *prelude,
+                                 const uint32_t *pos_host, const uint32_t *blocks_host,
+                                 size_t n_blocks, const uint32_t *table_at_host,
+                                 const float *sync_host, const uint32_t *sync_to_host,
+                                 size_t n_sync, float *out_host, uint32_t variant);
 
 /* Host-side block copy: lists in host memory, synchronous. */
 int32_t qvx_block_copy_host(qvx_device *dev, qvx_buffer *pool, const qvx_geometry *geo,

@@ -53,6 +53,8 @@ def lib() -> C.CDLL:
         L.qvo_rms_scale_of.argtypes = [C.c_float, C.c_float, C.c_float]
         L.qvo_rms_norm.argtypes = [P, P, C.c_size_t, C.c_double]
         L.qvo_rope_rotate.argtypes = [P, P, C.c_size_t]
+        L.qvo_attn_prelude.argtypes = [P, P, P, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_float, P, P,
+                                       C.c_double, P]
         L.qvo_f32_to_bf16.restype = C.c_uint16
         L.qvo_f32_to_bf16.argtypes = [C.c_float]
         L.qvo_bf16_to_f32.restype = C.c_float
@@ -140,6 +142,20 @@ def attend(q, k, v, pos: int) -> np.ndarray:
 def reduce_dot(w, x) -> float:
     w, x = _f32(w), _f32(x)
     return lib().qvo_reduce_dot(_p(w), _p(x), w.size)
+
+
+def attn_prelude(q, k_new, v_new, heads: int, kv_heads: int, d: int, rope, clip=None, qk_norm=None, eps: float = 1e-6):
+    """clip, full-width Q/K norms, RoPE (sim.rs:333-357) on copies of the raw projections: returns (q, k_new, v_new)."""
+    q, k_new, v_new = (np.array(a, dtype=np.float32, copy=True).reshape(-1) for a in (q, k_new, v_new))
+    s = k_new.size // (kv_heads * d)
+    rope = _f32(rope)
+    qn = kn = None
+    if qk_norm is not None:
+        qn, kn = _f32(qk_norm[0]), _f32(qk_norm[1])
+    lib().qvo_attn_prelude(_p(q), _p(k_new), _p(v_new), s, heads, kv_heads, d, 0 if clip is None else 1,
+                           0.0 if clip is None else float(clip), None if qn is None else _p(qn), None if kn is None else _p(kn),
+                           float(eps), _p(rope))
+    return q.reshape(s, heads, d), k_new.reshape(s, kv_heads * d), v_new.reshape(s, kv_heads * d)
 
 
 def block_bytes(geo: Geometry) -> int:

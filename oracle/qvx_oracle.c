@@ -159,6 +159,29 @@ void qvo_rope_rotate(float *head, const float *cs, size_t d) {
     }
 }
 
+/* crates/qubivex-backend-cpu/src/sim.rs:333-357 — what SimDevice::attention does to the raw
+ * projections: clamp(-c, c) on q, k and v (Rust's clamp: a NaN stays, -0 stays), the full-width
+ * norms of each token's q row and k row, RoPE on every head of q and k from the token's row. */
+static float clamp_rust(float z, float c) { return z < -c ? -c : (z > c ? c : z); }
+void qvo_attn_prelude(float *q, float *k_new, float *v_new, size_t s, size_t heads, size_t kvh, size_t d, int has_clip,
+                      float clip, const float *q_norm, const float *k_norm, double eps, const float *rope) {
+    size_t q_out = heads * d, kv_out = kvh * d;
+    if (has_clip) {
+        for (size_t i = 0; i < s * q_out; i++) q[i] = clamp_rust(q[i], clip);
+        for (size_t i = 0; i < s * kv_out; i++) k_new[i] = clamp_rust(k_new[i], clip);
+        for (size_t i = 0; i < s * kv_out; i++) v_new[i] = clamp_rust(v_new[i], clip);
+    }
+    if (q_norm && k_norm) {
+        for (size_t t = 0; t < s; t++) qvo_rms_norm(q + t * q_out, q_norm, q_out, eps);
+        for (size_t t = 0; t < s; t++) qvo_rms_norm(k_new + t * kv_out, k_norm, kv_out, eps);
+    }
+    for (size_t t = 0; t < s; t++) {
+        const float *cs = rope + t * d;
+        for (size_t h = 0; h < heads; h++) qvo_rope_rotate(q + t * q_out + h * d, cs, d);
+        for (size_t h = 0; h < kvh; h++) qvo_rope_rotate(k_new + t * kv_out + h * d, cs, d);
+    }
+}
+
 /* ================================================================================
  * Element conversion.  Widening bf16 is the reference's `bits << 16`
  * (crates/qubivex-backend-cpu/src/formats.rs:76-80).  Narrowing has no reference

@@ -26,6 +26,12 @@ class Config(C.Structure):
     _fields_ = [("device", C.c_int32), ("capacity", C.c_uint64), ("kv_pool", C.c_uint64), ("timing", C.c_uint32)]
 
 
+class Prelude(C.Structure):
+    """qvx_prelude: DeviceMoeAttention's clip / qk_norm / eps / rope (crates/qubivex-compute/src/discrete.rs:281-289)."""
+    _fields_ = [("has_clip", C.c_uint32), ("clip", C.c_float), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("eps", C.c_double), ("rope", C.c_void_p)]
+
+
 class Usage(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("capacity", "used", "peak", "refused")]
 
@@ -37,7 +43,7 @@ class TransferStats(C.Structure):
 
 
 K_COUNT = 6
-KERNEL_NAMES = ("sync", "append", "attn", "reduce", "exact", "copy")
+KERNEL_NAMES = ("sync", "append", "attn", "prelude", "exact", "copy")
 
 
 class KernelTimes(C.Structure):
@@ -100,6 +106,9 @@ PROTOTYPES = {
     "qvx_paged_attention_host_async": (C.c_int32, [P, P, _GEO, C.c_size_t, C.c_size_t, P, P, P, P, P, C.c_size_t, P,
                                                    P, P, C.c_size_t, P, C.c_uint32]),
     "qvx_wait": (C.c_int32, [P]),
+    "qvx_attn_prelude": (C.c_int32, [P, _GEO, C.c_size_t, C.c_size_t, P, P, P, C.POINTER(Prelude), P]),
+    "qvx_attention_stage_host": (C.c_int32, [P, P, _GEO, C.c_size_t, C.c_size_t, P, P, P, C.POINTER(Prelude), P, P, C.c_size_t,
+                                             P, P, P, C.c_size_t, P, C.c_uint32]),
     "qvx_block_copy_host": (C.c_int32, [P, P, _GEO, P, P, C.c_size_t]),
     "qvx_kvpool_blocks_for": (C.c_uint64, [_GEO, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int]),
     "qvx_kvpool_new": (P, [_GEO, C.c_uint32]),

@@ -33,6 +33,7 @@ SOURCES = {
     "attn_stream.cu": [],
     "attn_static.cu": [],
     "attn_exact.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],
+    "attn_prelude.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],
     "runtime.cpp": [],
 }
 

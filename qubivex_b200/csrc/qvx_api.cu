@@ -820,12 +820,23 @@ int32_t qvx_block_copy(qvx_device* dev, const qvx_geometry* geo, void* pool, siz
 }
 
 // ---- the op with host memory ----------------------------------------------------------------------
+static bool prelude_ok(const qvx_prelude* p) {
+    if (!p || !p->rope) return false;
+    if (p->has_clip && !(p->clip >= 0.0f)) return false;  // Rust's clamp(-c, c) panics on c < 0 or NaN
+    return (p->q_norm == nullptr) == (p->k_norm == nullptr);
+}
+
+// `pre` (host pointers), when given, runs the prelude on the staged q, k_new and v_new and copies
+// the new rows back into k_back / v_back.
 static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, size_t heads,
                                       size_t s, const float* q, const float* k_new, const float* v_new,
                                       const uint32_t* pos, const uint32_t* blocks, size_t n_blocks,
                                       const uint32_t* table_at, const float* sync, const uint32_t* sync_to,
-                                      size_t n_sync, float* out, uint32_t variant) {
+                                      size_t n_sync, float* out, uint32_t variant, const qvx_prelude* pre = nullptr,
+                                      float* k_back = nullptr, float* v_back = nullptr) {
     uint64_t t0 = now_ns();
+    if (pre && !prelude_ok(pre))
+        return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: a prelude needs a RoPE table, a clip >= 0 and both norms or neither");
     int32_t rc = buffer_of(dev, pool);
     if (rc) return rc;
     if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
@@ -850,9 +861,12 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     if (im.max_nch > MAX_CHUNKS) return too_many_chunks(dev, im.max_nch);
     // Staged on the device for this op: the tables image, sync_to, q, k_new, v_new, sync rows, out.
     auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const bool norms = pre && pre->q_norm;
     const size_t o_img = 0, o_syncto = o_img + im.bytes, o_q = o_syncto + up(4 * n_sync),
                  o_k = o_q + up(4 * s * q_out), o_v = o_k + up(4 * s * kv_out), o_sync = o_v + up(4 * s * kv_out),
-                 o_out = o_sync + up(8 * n_sync * kv_out), total = o_out + up(4 * s * q_out);
+                 o_out = o_sync + up(8 * n_sync * kv_out), o_rope = o_out + up(4 * s * q_out),
+                 o_qn = o_rope + (pre ? up(4 * s * L.d) : 0), o_kn = o_qn + (norms ? up(4 * q_out) : 0),
+                 total = o_kn + (norms ? up(4 * kv_out) : 0);
     DeviceExtras* x = extras(dev);
     size_t base = 0;
     rc = take_slice(dev, x, total, &base);
@@ -895,10 +909,22 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     copy_in(o_k, k_new, 4 * s * kv_out);
     copy_in(o_v, v_new, 4 * s * kv_out);
     copy_in(o_sync, sync, 8 * n_sync * kv_out);
+    if (pre) {
+        copy_in(o_rope, pre->rope, 4 * s * L.d);
+        if (norms) { copy_in(o_qn, pre->q_norm, 4 * q_out); copy_in(o_kn, pre->k_norm, 4 * kv_out); }
+    }
     if (e != cudaSuccess) return check_cuda(dev, e, "copy in");
     cudaEventRecord(op.in_done, h2d);
     cudaStreamWaitEvent(cs, op.in_done, 0);
 
+    if (pre && s) {  // clip, norms, RoPE on the staged projections: sim.rs:333-357
+        qvx_prelude dp = *pre;
+        dp.rope = (const float*)(ds + o_rope);
+        dp.q_norm = norms ? (const float*)(ds + o_qn) : nullptr;
+        dp.k_norm = norms ? (const float*)(ds + o_kn) : nullptr;
+        rc = launch_attn_prelude(dev, L, heads, s, (float*)(ds + o_q), (float*)(ds + o_k), (float*)(ds + o_v), &dp, cs);
+        if (rc) return rc;
+    }
     // sync rows, then the new rows, then attention: sim.rs:385-429.
     const float* d_sync = (const float*)(ds + o_sync);
     rc = launch_kv_rows(dev, L, pool->ptr, d_sync, d_sync + kv_out, 2 * kv_out, (const uint32_t*)(ds + o_syncto), nullptr,
@@ -911,6 +937,8 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     cudaStreamWaitEvent(d2h, op.kernels_done, 0);
     if (s) {
         e = cudaMemcpyAsync(out, ds + o_out, 4 * s * q_out, cudaMemcpyDeviceToHost, d2h);
+        if (e == cudaSuccess && k_back) e = cudaMemcpyAsync(k_back, ds + o_k, 4 * s * kv_out, cudaMemcpyDeviceToHost, d2h);
+        if (e == cudaSuccess && v_back) e = cudaMemcpyAsync(v_back, ds + o_v, 4 * s * kv_out, cudaMemcpyDeviceToHost, d2h);
         if (e != cudaSuccess) return check_cuda(dev, e, "copy out");
     }
     cudaEventRecord(op.out_done, d2h);
@@ -952,6 +980,33 @@ int32_t qvx_paged_attention_host(qvx_device* dev, qvx_buffer* pool, const qvx_ge
                                         sync, sync_to, n_sync, out, variant);
     int32_t rc2 = wait_locked(dev);
     return rc ? rc : rc2;
+}
+
+int32_t qvx_attention_stage_host(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, size_t heads, size_t s,
+                                 const float* q, float* k_new, float* v_new, const qvx_prelude* prelude, const uint32_t* pos,
+                                 const uint32_t* blocks, size_t n_blocks, const uint32_t* table_at, const float* sync,
+                                 const uint32_t* sync_to, size_t n_sync, float* out, uint32_t variant) {
+    if (!dev) return QVX_ERR_SHAPE;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    if (!prelude) return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: no prelude given");
+    int32_t rc = paged_attention_submit(dev, pool, geo, heads, s, q, k_new, v_new, pos, blocks, n_blocks, table_at, sync,
+                                        sync_to, n_sync, out, variant, prelude, k_new, v_new);
+    int32_t rc2 = wait_locked(dev);
+    return rc ? rc : rc2;
+}
+
+int32_t qvx_attn_prelude(qvx_device* dev, const qvx_geometry* geo, size_t heads, size_t s, float* q, float* k_new,
+                         float* v_new, const qvx_prelude* prelude, void* stream) {
+    if (!dev) return QVX_ERR_SHAPE;
+    if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
+    std::lock_guard<std::mutex> lk(dev->mu);
+    cudaSetDevice(dev->ordinal);
+    Layout L = make_layout(geo);
+    if (!prelude_ok(prelude) || heads == 0 || heads % L.kvh != 0 || (L.d & 1u))
+        return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: %zu tokens, %zu heads, %u KV heads of %u", s, heads,
+                    L.kvh, L.d);
+    return launch_attn_prelude(dev, L, heads, s, q, k_new, v_new, prelude, (cudaStream_t)stream);
 }
 
 int32_t qvx_block_copy_host(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, const uint32_t* src,

@@ -181,6 +181,8 @@ int32_t launch_kv_rows(qvx_device* dev, const Layout& L, void* pool, const float
                        const float* v_rows, size_t row_stride_f32, const uint32_t* at_direct,
                        const uint32_t* pos, const uint32_t* blocks, const uint32_t* table_at, size_t n,
                        int kind, cudaStream_t s);
+int32_t launch_attn_prelude(qvx_device* dev, const Layout& L, size_t heads, size_t s, float* q, float* k_new, float* v_new,
+                            const qvx_prelude* p, cudaStream_t stream);
 int32_t launch_block_copy(qvx_device* dev, const Layout& L, void* pool, const uint32_t* src,
                           const uint32_t* dst, size_t n, cudaStream_t s);
 

@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import _lib
-from ._lib import Config, Geometry, KernelTimes, TransferStats, Usage
+from ._lib import Config, Geometry, KernelTimes, Prelude, TransferStats, Usage
 
 F32, BF16, F16 = 0, 1, 2
 LAYOUT_REFERENCE, LAYOUT_NATIVE = 0, 1
@@ -218,6 +218,41 @@ class CudaDevice:
         if not wait:
             self._keep = getattr(self, "_keep", [])
             self._keep.append(keep)
+        return out
+
+    def attention_stage(self, pool: DeviceBuffer, geo: Geometry, heads: int, q, k_new, v_new, rope, pos, blocks, table_at,
+                        clip=None, qk_norm=None, eps: float = 1e-6, sync=None, sync_to=None, variant: int = ATTN_AUTO):
+        """DeviceMoeAttention after the projections (sim.rs:325-429): clip, full-width Q/K norms, RoPE, then the
+        sync rows, the new rows and attention.  k_new and v_new (f32 host arrays) are rewritten in place,
+        as the reference leaves them for the host cache; returns the attention outputs."""
+        pos = np.ascontiguousarray(pos, dtype=np.uint32)
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint32)
+        table_at = np.ascontiguousarray(table_at, dtype=np.uint32)
+        s, d = len(pos), geo.head_dim
+        kv_out = geo.kv_heads * d
+        n_sync = 0 if sync_to is None else len(sync_to)
+        if sync_to is not None:
+            sync_to = np.ascontiguousarray(sync_to, dtype=np.uint32)
+        rope = np.ascontiguousarray(rope, dtype=np.float32)
+        for a in (k_new, v_new):
+            if not (isinstance(a, np.ndarray) and a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]):
+                raise TypeError("k_new and v_new are written back: contiguous float32 arrays")
+        sizes_ok = (len(table_at) == s and rope.size == s * d and _numel(q) == s * heads * d and k_new.size == s * kv_out
+                    and v_new.size == s * kv_out and (0 if sync is None else _numel(sync)) == n_sync * 2 * kv_out)
+        qn = kn = None
+        if qk_norm is not None:
+            qn = np.ascontiguousarray(qk_norm[0], dtype=np.float32)
+            kn = np.ascontiguousarray(qk_norm[1], dtype=np.float32)
+            sizes_ok = sizes_ok and qn.size == heads * d and kn.size == kv_out
+        if not sizes_ok or heads % max(geo.kv_heads, 1) != 0:
+            raise ShapeError(f"shape mismatch in routed moe attention: {s} tokens, {heads} heads, "
+                             f"{geo.kv_heads} KV heads of {d}")
+        pre = Prelude(0 if clip is None else 1, 0.0 if clip is None else float(clip),
+                      None if qn is None else qn.ctypes.data, None if kn is None else kn.ctypes.data, float(eps), rope.ctypes.data)
+        out = np.empty((s, heads, d), dtype=np.float32)
+        self.check(self.lib.qvx_attention_stage_host(self.h, pool.handle, C.byref(geo), heads, s, ptr(q), ptr(k_new), ptr(v_new),
+                                                     C.byref(pre), ptr(pos), ptr(blocks), len(blocks), ptr(table_at), ptr(sync),
+                                                     ptr(sync_to), n_sync, ptr(out), variant))
         return out
 
     def wait(self) -> None:

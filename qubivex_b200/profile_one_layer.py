@@ -56,7 +56,6 @@ for variant in (qd.ATTN_SPLIT,):
     kt = dev.kernel_times()
     byts = wl.algorithmic_bytes(shape, lengths)
     a = kt["attn"][1] / kt["attn"][0] * 1e-9
-    r = kt["reduce"][1] / max(kt["reduce"][0], 1) * 1e-9
-    print(f"perm={os.environ.get('PERM','random')} B={shape.block_tokens} chunk={os.environ.get('QVX_CHUNK_TOKENS', '256')} batch={batch} bytes={byts/2**20:.1f} MiB attn={a*1e6:.1f} us reduce={r*1e6:.1f} us "
-          f"wall/iter={wall*1e6:.1f} us -> attn {byts/a/1e9:.0f} GB/s, attn+reduce {byts/(a+r)/1e9:.0f} GB/s, wall {byts/wall/1e9:.0f} GB/s")
+    print(f"blocks={os.environ.get('PERM', 'random')} B={shape.block_tokens} batch={batch} bytes={byts / 2**20:.1f} MiB attn={a * 1e6:.1f} us "
+          f"wall/iter={wall * 1e6:.1f} us -> attn {byts / a / 1e9:.0f} GB/s, wall {byts / wall / 1e9:.0f} GB/s")
 dev.close()

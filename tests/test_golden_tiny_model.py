@@ -58,7 +58,19 @@ def oracle_decode(heads, kvh, d, q, k, v):
     return out, pool
 
 
-def attention_stage(name, layer, decode):
+def rope_table(T, d, theta):
+    """One row [cos.., sin..] per position, as the host hands it to the device (DeviceMoeAttention::rope)."""
+    inv = (1.0 / (np.float32(theta) ** (np.arange(0, d, 2, dtype=np.float32) / np.float32(d)))).astype(np.float32)
+    rows = np.empty((T, d), dtype=np.float32)
+    for p in range(T):
+        f = (np.float32(p) * inv).astype(np.float32)
+        rows[p] = np.concatenate([np.cos(f), np.sin(f)])
+    return rows
+
+
+def attention_stage(name, layer, decode, stage=None):
+    """`decode` takes normed, rotated q / k / v; `stage`, if given, takes the raw projections with the
+    norm weights and the RoPE table instead (the prelude is then part of what is under test)."""
     hidden, heads, kvh, d, _ = (int(x) for x in G[f"{name}/meta"])
     eps, theta = (float(x) for x in G[f"{name}/eps_theta"])
     x = G[f"{name}/embed"] if layer == 0 else G[f"{name}/{layer - 1}/hidden"]
@@ -67,11 +79,21 @@ def attention_stage(name, layer, decode):
     q = (h @ G[key + "q_proj"].T).astype(np.float32)
     k = (h @ G[key + "k_proj"].T).astype(np.float32)
     v = (h @ G[key + "v_proj"].T).astype(np.float32)
-    if key + "q_norm" in G:
-        q, k = rms_rows(q, G[key + "q_norm"], eps), rms_rows(k, G[key + "k_norm"], eps)
-    q, k = rope_rows(q, heads, d, theta), rope_rows(k, kvh, d, theta)
-    att = decode(heads, kvh, d, q, k, v)
+    if stage is not None:
+        norms = (G[key + "q_norm"], G[key + "k_norm"]) if key + "q_norm" in G else None
+        att = stage(heads, kvh, d, q, k, v, rope_table(q.shape[0], d, theta), norms, eps)
+    else:
+        if key + "q_norm" in G:
+            q, k = rms_rows(q, G[key + "q_norm"], eps), rms_rows(k, G[key + "k_norm"], eps)
+        q, k = rope_rows(q, heads, d, theta), rope_rows(k, kvh, d, theta)
+        att = decode(heads, kvh, d, q, k, v)
     return (att.reshape(att.shape[0], heads * d) @ G[key + "o_proj"].T).astype(np.float32), G[key + "attention"]
+
+
+def oracle_stage(heads, kvh, d, q, k, v, rope, norms, eps):
+    """The oracle's prelude (clip none, the model's norms, RoPE), then its paged decode."""
+    q2, k2, v2 = oracle.attn_prelude(q, k, v, heads, kvh, d, rope, qk_norm=norms, eps=eps)
+    return oracle_decode(heads, kvh, d, q2.reshape(-1, heads * d), k2, v2)[0]
 
 
 CASES = [("dense-tiny", 0), ("dense-tiny", 1), ("olmoe-tiny", 0), ("olmoe-tiny", 1)]
@@ -80,6 +102,43 @@ CASES = [("dense-tiny", 0), ("dense-tiny", 1), ("olmoe-tiny", 0), ("olmoe-tiny",
 @pytest.mark.parametrize("name,layer", CASES)
 def test_the_oracle_reproduces_the_references_attention_outputs(name, layer):
     ours, want = attention_stage(name, layer, lambda *a: oracle_decode(*a)[0])
+    assert rel(ours, want) <= TOL, rel(ours, want)
+
+
+@pytest.mark.parametrize("name,layer", CASES)
+def test_the_oracles_prelude_reproduces_them_too(name, layer):
+    ours, want = attention_stage(name, layer, None, stage=oracle_stage)
+    assert rel(ours, want) <= TOL, rel(ours, want)
+    plain, _ = attention_stage(name, layer, lambda *a: oracle_decode(*a)[0])
+    assert np.array_equal(ours.view(np.uint32), plain.view(np.uint32))  # one prelude call = norm rows, then rotate rows
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,layer", CASES)
+def test_the_cuda_stage_with_its_prelude_reproduces_them(dev, name, layer):
+    from qubivex_b200 import device as qd
+
+    def device_stage(heads, kvh, d, q, k, v, rope, norms, eps):
+        geo = qd.geometry(KV_BLOCK, kvh, d, qd.F32, qd.LAYOUT_REFERENCE)
+        n = 2 * qd.block_bytes(geo)
+        buf = dev.alloc(n)
+        dev.write(buf, 0, np.zeros(n, dtype=np.uint8))
+        T = q.shape[0]
+        out = np.zeros((T, heads, d), dtype=np.float32)
+        k_back, v_back = np.array(k, copy=True), np.array(v, copy=True)
+        for p in range(T):
+            out[p] = dev.attention_stage(buf, geo, heads, q[p:p + 1], k_back[p:p + 1], v_back[p:p + 1], rope[p:p + 1], [p], [1], [0],
+                                         qk_norm=norms, eps=eps)[0]
+        q2, k2, v2 = oracle.attn_prelude(q, k, v, heads, kvh, d, rope, qk_norm=norms, eps=eps)
+        want_att, want_pool = oracle_decode(heads, kvh, d, q2.reshape(-1, heads * d), k2, v2)
+        assert np.array_equal(k_back.view(np.uint32), k2.view(np.uint32))       # the rows the host cache keeps
+        assert np.array_equal(v_back.view(np.uint32), v2.view(np.uint32))
+        assert np.array_equal(out.view(np.uint32), want_att.view(np.uint32))
+        assert np.array_equal(dev.read(buf, 0, n), want_pool)
+        buf.free()
+        return out
+
+    ours, want = attention_stage(name, layer, None, stage=device_stage)
     assert rel(ours, want) <= TOL, rel(ours, want)
 
 
