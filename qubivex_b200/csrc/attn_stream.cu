@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 }
                 return true;
             };
-            const bool last_chunk = rec[4] == NO_PART || rec[4] - rec[5] == rec[6] - 1;
+            const bool last_chunk = rec[4] == NO_PART || rec[4] - rec[5] + rec[9] == rec[6];  // the run ends the sequence
             uint32_t tau0 = 0;
             if (k == 0 && a.overlap) {
                 // The first item's old positions stream while the stream's earlier work finishes;
@@ -683,9 +683,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     const bool tr = lane == 0 && (warp == 0 || warp == CW - 1);
 #endif
     bool dead = false;    // this warp gave up a wait
+    uint32_t kc = 0;      // chunks handed over so far, over all items
     for (uint32_t k = 0;; k++) {
-        const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS, ms = k % MAIL_SLOTS;
+        const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
         Item it{};
+        uint32_t chunk_tokens = 0, run = 1;
         if (!dead && !__all_sync(0xffffffffu, mbar_wait(qfull0 + qslot * 8, (k / Q_SLOTS) & 1))) dead = true;
         // The record came by bulk copy: observe its own barrier too before reading it.
         if (!dead && !__all_sync(0xffffffffu, mbar_wait(recbar0 + rslot * 8, (k / REC_SLOTS) & 1))) dead = true;
@@ -693,6 +695,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             const uint32_t* rec = reinterpret_cast<const uint32_t*>(smem + SM::rec_off) + rslot * REC_WORDS;
             it.seq = rec[0]; it.tokens = rec[1]; it.head0 = rec[2]; it.nheads = rec[3] & 0xffffu; it.kv_head = rec[3] >> 16;
             it.part = rec[4]; it.part0 = rec[5]; it.nch = rec[6]; it.counter = rec[7];
+            chunk_tokens = rec[8]; run = rec[9];
         }
         if (dead) {
             // Every other wait in the CTA is bounded too: the others give up in their turn.
@@ -700,33 +703,23 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
         }
-        // The epilogue warp learns of the item now (or of the end of the queue).  It has finished
-        // item k - 3 at least -- the state buffers are handed over two at a time -- so note slot
-        // k % NOTE_SLOTS is free.
-        if (warp == 0 && lane == 0) {
-            const uint32_t ns = k % NOTE_SLOTS;
-            mailbox[ns].seq = it.seq; mailbox[ns].head0 = it.head0; mailbox[ns].nheads = it.nheads;
-            mailbox[ns].part0 = it.part0; mailbox[ns].nch = it.nch; mailbox[ns].counter = it.counter;
-            mailbox[ns].stop = it.tokens == 0 ? 1u : 0u;
-            mailbox[ns].chunk = it.part == NO_PART ? NO_PART : it.part - it.part0;
-            mbar_arrive(note0 + ns * 8);
+        // The epilogue warp learns of every chunk when the consumers start it (below), and of the
+        // end of the queue here.  It has finished chunk kc - 3 at least -- the state buffers are
+        // handed over two at a time -- so note slot kc % NOTE_SLOTS is free.
+        if (it.tokens == 0) {  // the end of the queue: every consumer warp reads the same record
+            if (warp == 0 && lane == 0) {
+                const uint32_t ns = kc % NOTE_SLOTS;
+                mailbox[ns].stop = 1u;
+                mbar_arrive(note0 + ns * 8);
+            }
+            return;
         }
-        if (it.tokens == 0) return;  // the end of the queue: every consumer warp reads the same record
 #ifdef QVX_TRACE
         if (tr) TRACE(tp, 20);  // item header read
 #endif
-        // Tiles are dealt to the warps by their number in the whole stream; this warp takes the
-        // item's tiles first, first + CW, ...  Its state goes to place `first` of the buffer, so
-        // the merge runs in the order of the tiles' places in the item and the sum order does not
-        // depend on how many tiles this CTA happened to stream before the item.
-        const uint32_t first = (warp + CW - nbase % CW) % CW;
-        float o[D / 16][4];
-#pragma unroll
-        for (int m = 0; m < D / 16; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; }
-        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // heads 2t and 2t+1
-        if (!dead) {
-            // Q^T fragments (the B operand): this lane holds head g, dims 16*ks + 2t + {0,1,8,9}.
-            uint32_t qf[D / 16][2], ql[D / 16][2];
+        // Q^T fragments (the B operand), once per item: this lane holds head g, dims 16*ks + 2t + {0,1,8,9}.
+        uint32_t qf[D / 16][2], ql[D / 16][2];
+        {
             {
                 const bool live = g < it.nheads;
                 const float* qrow = reinterpret_cast<const float*>(smem + SM::q_off + (qslot * 8 + g) * SM::q_stride);
@@ -743,14 +736,38 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(qempty0 + qslot * 8);  // the producer may reuse this query slot
-
-            const uint32_t ntiles = (it.tokens + TILE - 1) / TILE;
+        }
+        // The item's chunks, one after the other: each has its own state and its own hand-over, so
+        // its result is what it would be as an item of its own; the queries, the record and the
+        // producer's set-up are shared by the run.
+        for (uint32_t j = 0; j < run; j++, kc++) {
+        const uint32_t ms = kc % MAIL_SLOTS;
+        const uint32_t ctokens = min(chunk_tokens, it.tokens - j * chunk_tokens);
+        if (warp == 0 && lane == 0) {
+            const uint32_t ns = kc % NOTE_SLOTS;
+            mailbox[ns].seq = it.seq; mailbox[ns].head0 = it.head0; mailbox[ns].nheads = it.nheads;
+            mailbox[ns].part0 = it.part0; mailbox[ns].nch = it.nch; mailbox[ns].counter = it.counter;
+            mailbox[ns].stop = 0u;
+            mailbox[ns].chunk = it.part == NO_PART ? NO_PART : it.part - it.part0 + j;
+            mbar_arrive(note0 + ns * 8);
+        }
+        // Tiles are dealt to the warps by their number in the whole stream; this warp takes the
+        // chunk's tiles first, first + CW, ...  Its state goes to place `first` of the buffer, so
+        // the merge runs in the order of the tiles' places in the chunk and the sum order does not
+        // depend on how many tiles this CTA happened to stream before it.
+        const uint32_t first = (warp + CW - nbase % CW) % CW;
+        float o[D / 16][4];
+#pragma unroll
+        for (int m = 0; m < D / 16; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; }
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // heads 2t and 2t+1
+        {
+            const uint32_t ntiles = (ctokens + TILE - 1) / TILE;
             for (uint32_t tau = first; tau < ntiles; tau += CW) {
                 const uint32_t n = nbase + tau;
                 const uint32_t st = n % SM::stages, ph = (n / SM::stages) & 1;
                 if (!__all_sync(0xffffffffu, mbar_wait(full0 + st * 8, ph))) { dead = true; break; }
                 const uint32_t kt = sbase + SM::ring_off + st * SM::stage_bytes, vt = kt + SM::tile_bytes;
-                const uint32_t valid = min((uint32_t)TILE, it.tokens - tau * TILE);
+                const uint32_t valid = min((uint32_t)TILE, ctokens - tau * TILE);
 #ifndef QVX_EXPERIMENT_NOCOMPUTE
                 // S^T = K Q^T; the value pass and the remainder pass accumulate separately so the
                 // chain of dependent tensor-core ops is half as long.
@@ -828,7 +845,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         }
         // ---- this warp's state goes to the epilogue warp, and the warp goes on -------------------
         // The buffer is free once the epilogue warp has merged the item two before this one.
-        if (!__all_sync(0xffffffffu, mbar_wait(rfree0 + ms * 8, ((k / MAIL_SLOTS) & 1) ^ 1))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(rfree0 + ms * 8, ((kc / MAIL_SLOTS) & 1) ^ 1))) {
             *abort_flag = 1;
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
@@ -850,6 +867,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
 #ifdef QVX_TRACE
         if (tr) TRACE(tp, 23);  // state handed over
 #endif
+        }  // chunks of the item
     }
 }
 

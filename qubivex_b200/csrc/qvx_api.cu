@@ -274,6 +274,21 @@ static uint32_t chunk_tokens_for(const Layout& L, uint32_t len) {
     return c;
 }
 
+// How many consecutive chunks of a (sequence, group) make one work item.  A chunk's result does
+// not depend on it (the kernel keeps one state per chunk whatever run it streams it in), so
+// unlike the chunk size this may look at the whole op: with many chunks per resident CTA the
+// items grow, and what a CTA pays per item (the next record, the query rows, the queue) is paid
+// less often; with few, items stay single chunks and the queue evens the CTAs out.  A run never
+// exceeds RUN_TOKENS positions (its block ids ride in the item's record).
+static const uint32_t RUN_TOKENS = 2048;
+static uint32_t run_chunks_for(size_t total_chunks, uint32_t resident_ctas) {
+    const char* v = getenv("QVX_RUN_CHUNKS");  // experiments and tests: a fixed run length (read at every op)
+    const long configured = v ? atol(v) : 0;
+    if (configured > 0) return (uint32_t)configured;
+    const size_t per_cta = total_chunks / std::max(1u, resident_ctas);
+    return (uint32_t)std::min<size_t>(4, std::max<size_t>(1, per_cta / 6));
+}
+
 // The CTA that merges a sequence's splits keeps every split's maximum and row sum in shared
 // memory: 64 bytes per split of the 64 KiB a CTA always has.
 constexpr size_t MAX_CHUNKS = 1000;
@@ -286,7 +301,7 @@ static int32_t too_many_chunks(qvx_device* dev, size_t nch) {
 struct TableImage {
     size_t off_pos, off_table_at, off_blocks, off_items, bytes;
     size_t n_items, n_parts, n_counters, max_nch;
-    uint32_t max_pos, chunk_blocks, item_words;
+    uint32_t max_pos, chunk_blocks, item_words, run;
 };
 
 static int32_t validate_tables(qvx_device* dev, const Layout& L, size_t pool_blocks, size_t heads, size_t s,
@@ -314,15 +329,16 @@ struct PlanCache {
     uint32_t B = 0, kvh = 0, d = 0, dtype = 0, layout = 0;
     size_t heads = 0, s = 0;
     bool split = false;
+    uint32_t ctas = 0;
     std::vector<uint32_t> pos;
     TableImage im{};                       // counts and sizes; the offsets depend on n_blocks and are redone
     std::vector<qvx_item_header> headers;  // in launch order
     std::vector<uint32_t> seq_off, count;  // per item: first block's offset in its sequence's table, blocks
 };
 
-static bool plan_hit(const PlanCache* c, const Layout& L, size_t heads, size_t s, const uint32_t* pos, bool split) {
+static bool plan_hit(const PlanCache* c, const Layout& L, size_t heads, size_t s, const uint32_t* pos, bool split, uint32_t ctas) {
     return c && c->valid && c->B == L.B && c->kvh == L.kvh && c->d == L.d && c->dtype == L.dtype && c->layout == L.layout &&
-           c->heads == heads && c->s == s && c->split == split && memcmp(c->pos.data(), pos, 4 * s) == 0;
+           c->heads == heads && c->s == s && c->split == split && c->ctas == ctas && memcmp(c->pos.data(), pos, 4 * s) == 0;
 }
 
 static void image_offsets(TableImage& im, size_t s, size_t n_blocks) {
@@ -335,9 +351,31 @@ static void image_offsets(TableImage& im, size_t s, size_t n_blocks) {
     im.bytes = (off + 255) & ~(size_t)255;
 }
 
+// The runs a (sequence, group) of `nch` chunks is cut into, given the op's run length: runs of
+// `run` chunks from the front; the last `tail` chunks stay single, so that the end of the launch
+// has small items to even the CTAs out with.  Calls f(first chunk, chunks).
+static uint32_t run_tail_chunks() {
+    const char* v = getenv("QVX_RUN_TAIL");  // experiments
+    return v ? (uint32_t)atol(v) : 0u;
+}
+template <typename F>
+static void for_each_run(uint32_t nch, uint32_t run, uint32_t tail, F f) {
+    const uint32_t singles = run > 1 ? std::min(nch, tail) : 0u, front = nch - singles;
+    for (uint32_t c = 0; c < front; c += run) f(c, std::min(run, front - c));
+    for (uint32_t c = front; c < nch; c++) f(c, 1u);
+}
+
+// CTAs of the streaming attention kernel the device keeps resident for this geometry; 0 when another
+// kernel serves it (one CTA per item there: items stay single chunks).
+static uint32_t stream_ctas(const qvx_device* dev, const Layout& L, size_t heads) {
+    if (L.dtype == QVX_F32 || !attn_split_supported(L, heads)) return 0;
+    return (uint32_t)dev->prop.multiProcessorCount * (L.d <= 128 ? 2u : 1u);
+}
+
+// `ctas`: stream_ctas() of the device.
 static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint32_t* pos, size_t n_blocks,
-                             bool split, PlanCache* cache = nullptr) {
-    if (plan_hit(cache, L, heads, s, pos, split)) {
+                             bool split, uint32_t ctas, PlanCache* cache = nullptr) {
+    if (plan_hit(cache, L, heads, s, pos, split, ctas)) {
         TableImage im = cache->im;
         image_offsets(im, s, n_blocks);
         return im;
@@ -346,18 +384,28 @@ static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint
     TableImage im{};
     size_t group = heads / L.kvh, groups = L.kvh * ((group + 7) / 8);
     im.chunk_blocks = 1;
+    size_t total_chunks = 0;
     for (size_t t = 0; t < s; t++) {
         im.max_pos = std::max(im.max_pos, pos[t]);
         if (!split) continue;
         const uint32_t chunk = chunk_tokens_for(L, pos[t] + 1u);
-        im.chunk_blocks = std::max(im.chunk_blocks, chunk / L.B);
         size_t nch = ((size_t)pos[t] + chunk) / chunk;
         im.max_nch = std::max<size_t>(im.max_nch, nch);
-        im.n_items += nch * groups;
+        total_chunks += nch * groups;
         if (nch > 1) {
             im.n_parts += (size_t)attn_parts_per_group(L, (uint32_t)nch) * groups;
             im.n_counters += (size_t)attn_counters_per_group(L, (uint32_t)nch) * groups;
         }
+    }
+    im.run = split && ctas ? run_chunks_for(total_chunks, ctas) : 1u;
+    for (size_t t = 0; split && t < s; t++) {
+        const uint32_t chunk = chunk_tokens_for(L, pos[t] + 1u);
+        const uint32_t nch = (uint32_t)(((size_t)pos[t] + chunk) / chunk);
+        const uint32_t run = std::min(nch, std::max(1u, std::min(im.run, RUN_TOKENS / chunk)));
+        im.chunk_blocks = std::max(im.chunk_blocks, run * (chunk / L.B));
+        size_t runs = 0;
+        for_each_run(nch, run, run_tail_chunks(), [&](uint32_t, uint32_t) { runs++; });
+        im.n_items += runs * groups;
     }
     im.item_words = (QVX_ITEM_HEADER_WORDS + im.chunk_blocks + 3u) & ~3u;
     image_offsets(im, s, n_blocks);
@@ -366,13 +414,13 @@ static TableImage plan_image(const Layout& L, size_t heads, size_t s, const uint
 
 static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size_t heads, size_t s,
                        const uint32_t* pos, const uint32_t* blocks, size_t n_blocks, const uint32_t* table_at,
-                       PlanCache* cache = nullptr, bool split = true) {
+                       uint32_t ctas, PlanCache* cache = nullptr, bool split = true) {
     memcpy(img + im.off_pos, pos, 4 * s);
     memcpy(img + im.off_table_at, table_at, 4 * s);
     memcpy(img + im.off_blocks, blocks, 4 * n_blocks);
     if (im.n_items == 0) return;
     const uint32_t id_words = im.item_words - QVX_ITEM_HEADER_WORDS;
-    if (plan_hit(cache, L, heads, s, pos, split)) {
+    if (plan_hit(cache, L, heads, s, pos, split, ctas)) {
         uint32_t* items = (uint32_t*)(img + im.off_items);
         for (size_t n = 0; n < cache->headers.size(); n++) {
             uint32_t* w = items + n * im.item_words;
@@ -386,7 +434,7 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     }
     if (cache) {
         cache->B = L.B; cache->kvh = L.kvh; cache->d = L.d; cache->dtype = L.dtype; cache->layout = L.layout;
-        cache->heads = heads; cache->s = s; cache->split = split;
+        cache->heads = heads; cache->s = s; cache->split = split; cache->ctas = ctas;
         cache->pos.assign(pos, pos + s);
         cache->im = im;
         cache->headers.resize(im.n_items); cache->seq_off.resize(im.n_items); cache->count.resize(im.n_items);
@@ -395,19 +443,22 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     const uint32_t group = (uint32_t)(heads / L.kvh), gpk = (group + 7) / 8, groups = L.kvh * gpk;
     // Longest first, so the short tails fill the end of the launch.  The order is a function
     // of the lengths alone: a counting sort by tokens, ties in (sequence, group, chunk) order.
-    struct Key { uint32_t tokens, seq, grp, c; };
+    struct Key { uint32_t tokens, seq, grp, c, run; };
     std::vector<Key> keys;
     keys.reserve(im.n_items);
     std::vector<uint32_t> part_base(s), counter_base(s);
     uint32_t part = 0, counter = 0;
     for (size_t t = 0; t < s; t++) {
         const uint32_t len = pos[t] + 1u, chunk = chunk_tokens_for(L, len), nch = (len + chunk - 1) / chunk;
+        const uint32_t run = std::min(nch, std::max(1u, std::min(im.run, RUN_TOKENS / chunk)));
         part_base[t] = part; counter_base[t] = counter;
         if (nch > 1) { part += attn_parts_per_group(L, nch) * groups; counter += attn_counters_per_group(L, nch) * groups; }
         for (uint32_t grp = 0; grp < groups; grp++)
-            for (uint32_t c = 0; c < nch; c++) keys.push_back(Key{std::min(chunk, len - c * chunk), (uint32_t)t, grp, c});
+            for_each_run(nch, run, run_tail_chunks(), [&](uint32_t c, uint32_t r) {
+                keys.push_back(Key{std::min(len, (c + r) * chunk) - c * chunk, (uint32_t)t, grp, c, r});
+            });
     }
-    // (a counting sort: tokens <= chunk, and this runs once per op on the host's critical path)
+    // (a counting sort: tokens <= max_chunk, and this runs once per op on the host's critical path)
     std::vector<uint32_t> start(max_chunk + 2, 0);
     for (const Key& k : keys) start[max_chunk - k.tokens + 1]++;
     for (uint32_t v = 0; v <= max_chunk; v++) start[v + 1] += start[v];
@@ -419,7 +470,7 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
         const uint32_t t = k.seq, len = pos[t] + 1u, chunk = chunk_tokens_for(L, len), nch = (len + chunk - 1) / chunk;
         uint32_t kvh = k.grp / gpk, sub = k.grp % gpk;
         uint32_t* w = items + n * im.item_words;
-        qvx_item_header h;
+        qvx_item_header h{};
         h.seq = t;
         h.tokens = k.tokens;
         h.head0 = kvh * group + sub * 8;
@@ -428,6 +479,8 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
         h.part = nch > 1 ? h.part0 + k.c : 0xffffffffu;
         h.nch = nch;
         h.counter = nch > 1 ? counter_base[t] + k.grp * attn_counters_per_group(L, nch) : 0;  // the group's first arrival counter
+        h.chunk_tokens = chunk;
+        h.run = k.run;
         memcpy(w, &h, sizeof h);
         uint32_t count = (k.tokens + L.B - 1) / L.B;
         const uint32_t* src = blocks + table_at[t] + (size_t)k.c * (chunk / L.B);
@@ -760,10 +813,11 @@ int32_t qvx_tables_create(qvx_device* dev, const qvx_geometry* geo, size_t pool_
     Layout L = make_layout(geo);
     int32_t rc = validate_tables(dev, L, pool_blocks, heads, s, pos, blocks, n_blocks, table_at);
     if (rc) return rc;
-    TableImage im = plan_image(L, heads, s, pos, n_blocks, attn_split_supported(L, heads));
+    const uint32_t ctas = stream_ctas(dev, L, heads);
+    TableImage im = plan_image(L, heads, s, pos, n_blocks, attn_split_supported(L, heads), ctas);
     if (im.max_nch > MAX_CHUNKS) return too_many_chunks(dev, im.max_nch);
     std::vector<uint8_t> img(im.bytes);
-    fill_image(im, img.data(), L, heads, s, pos, blocks, n_blocks, table_at);
+    fill_image(im, img.data(), L, heads, s, pos, blocks, n_blocks, table_at, ctas);
     void* d = nullptr;
     cudaError_t e = cudaMalloc(&d, im.bytes);
     if (e != cudaSuccess) return check_cuda(dev, e, "tables");
@@ -857,7 +911,8 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     variant &= 0xffu;  // the host op orders its own copies and kernels: no overlap with what precedes it
     if (!dev->plan_cache) dev->plan_cache = new PlanCache;
     PlanCache* cache = static_cast<PlanCache*>(dev->plan_cache);
-    TableImage im = plan_image(L, heads, s, pos, n_blocks, split, cache);
+    const uint32_t ctas = stream_ctas(dev, L, heads);
+    TableImage im = plan_image(L, heads, s, pos, n_blocks, split, ctas, cache);
     if (im.max_nch > MAX_CHUNKS) return too_many_chunks(dev, im.max_nch);
     // Staged on the device for this op: the tables image, sync_to, q, k_new, v_new, sync rows, out.
     auto up = [](size_t b) { return (b + 255) & ~(size_t)255; };
@@ -879,7 +934,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     op.begin = base; op.end = base + total;
     op.in_done = take_event(x); op.kernels_done = take_event(x); op.out_done = take_event(x);
 
-    fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at, cache, split);
+    fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at, ctas, cache, split);
     // A position listed twice: the later row wins (the reference writes them in list order).
     uint32_t* st = (uint32_t*)(hs + o_syncto);
     {

@@ -192,16 +192,21 @@ int32_t launch_block_copy(qvx_device* dev, const Layout& L, void* pool, const ui
 // (kv head, group of <= 8 query heads).  In device memory an item is ITEM_HEADER_WORDS
 // 32-bit words followed by the ids of its blocks, so that one round trip brings a CTA
 // everything it needs to start its copies.
-#define QVX_ITEM_HEADER_WORDS 8
+// A work item: a run of consecutive chunks of one (sequence, group of query heads).  A chunk's
+// result is the same whatever run it is part of; runs only say how the chunks are dealt out.
+#define QVX_ITEM_HEADER_WORDS 12
 struct qvx_item_header {
     uint32_t seq;
     uint32_t tokens;      // valid positions in this item (the last block may be partly filled)
     uint32_t head0;       // first query head of the group
     uint32_t nheads_kv;   // query heads in the group (<= 8) | kv head << 16
-    uint32_t part;        // index of this item's partial result; 0xffffffff: write `out` directly
+    uint32_t part;        // index of the partial result of the item's first chunk; 0xffffffff: write `out` directly
     uint32_t part0;       // the partial of the first chunk of this (sequence, group)
     uint32_t nch;         // chunks of this (sequence, group)
-    uint32_t counter;     // which arrival counter the chunks of this (sequence, group) share
+    uint32_t counter;     // which arrival counters the chunks of this (sequence, group) share
+    uint32_t chunk_tokens;  // positions per chunk of this sequence (its last chunk may hold fewer)
+    uint32_t run;           // chunks in this item
+    uint32_t reserved[2];
 };
 
 struct qvx_tables {

@@ -388,3 +388,21 @@ def test_batch_invariance_when_ctas_stream_many_ragged_items(dev):
         alone.sync_to = full.sync_to[lo:lo + n - 1]
         _, out_alone = alone.run_device(dev, variant=qd.ATTN_SPLIT)
         assert np.array_equal(out_alone[0].view(np.uint32), out_full[t].view(np.uint32)), t
+
+
+def test_runs_of_chunks_do_not_change_a_single_bit(dev, monkeypatch):
+    # Work items are runs of consecutive chunks of a sequence; how long the runs are is the
+    # scheduler's choice per op.  Every chunk keeps its own state, so the outputs must not move.
+    lengths = [3000, 513, 2048, 1, 1537, 4096, 700, 2049] * 3
+    c = Case(32, 4, 128, 16, "bf16", lengths, seed=95, amp_qk=0.4)
+    outs = {}
+    for run in ("1", "2", "3", "4"):
+        monkeypatch.setenv("QVX_RUN_CHUNKS", run)
+        outs[run] = c.run_device(dev, variant=qd.ATTN_SPLIT)[1]
+    monkeypatch.delenv("QVX_RUN_CHUNKS")
+    outs["auto"] = c.run_device(dev, variant=qd.ATTN_SPLIT)[1]
+    for k, v in outs.items():
+        assert np.array_equal(v.view(np.uint32), outs["1"].view(np.uint32)), k
+    _, want = c.run_oracle()
+    ok, err = within(outs["4"], want, "bf16")
+    assert ok, err
