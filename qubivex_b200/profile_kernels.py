@@ -94,7 +94,11 @@ def rows_case(dev, name, shape: wl.Shape, n_rows, dtype=qd.BF16):
     pool_blocks = n_rows // shape.block_tokens + 2
     pool = torch.empty(pool_blocks * bb, dtype=torch.uint8, device="cuda")
     rows = torch.randn((n_rows, 2 * shape.kv_out), device="cuda")
-    to = torch.from_numpy(np.random.default_rng(1).permutation(n_rows).astype(np.int32)).cuda()
+    # rows arrive in position order (a prefill's sync rows); their blocks are scattered over the pool
+    B = shape.block_tokens
+    block_of = np.random.default_rng(1).permutation(pool_blocks)[: (n_rows + B - 1) // B].astype(np.int64)
+    row = np.arange(n_rows, dtype=np.int64)
+    to = torch.from_numpy((block_of[row // B] * B + row % B).astype(np.int32)).cuda()
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     sec = _time(dev, lambda: dev.check(dev.lib.qvx_kv_sync(dev.h, C.byref(geo), ptr(pool), pool_blocks, ptr(rows), ptr(to), n_rows, stream)), "sync")
     e = 4 if dtype == qd.F32 else 2
