@@ -262,10 +262,12 @@ __device__ __forceinline__ bool fold_ahead(const StreamArgs& a, const Mail& it, 
     const uint32_t node = it.chunk / MERGE_FAN, first = node * MERGE_FAN, size = min(MERGE_FAN, it.nch - first), mine = it.chunk - first;
     if (size < 2) return false;
     const uint32_t* claimed = a.counters + it.counter + 2 * node;
-    uint32_t others = 0;
-    if (lane == 0) others = *reinterpret_cast<const volatile uint32_t*>(claimed);
-    if (__shfl_sync(0xffffffffu, others, 0) != size - 1) return false;
-    if (!wait_published(claimed + 1, size - 1)) return false;  // the caller's own wait reports a failure
+    // Both words in one round trip: lane 0 reads `claimed`, lane 1 `published`.
+    uint32_t word = 0;
+    if (lane < 2) word = *reinterpret_cast<const volatile uint32_t*>(claimed + lane);
+    if (__shfl_sync(0xffffffffu, word, 0) != size - 1) return false;
+    if (__shfl_sync(0xffffffffu, word, 1) != size - 1 && !wait_published(claimed + 1, size - 1))
+        return false;  // the caller's own wait reports a failure
     fence_acq_rel_gpu();
     r.clear();
     float4 none[8 * D / 4 / 32];
@@ -317,8 +319,9 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
 #endif
             if (!last) {
                 float* pe = p0 + (size_t)mine * PART_STRIDE;
+                const uint64_t keep = l2_policy_evict_last();  // read again by the node's last arrival: stay in the L2
 #pragma unroll
-                for (int j = 0; j < NJ; j++) *reinterpret_cast<float4*>(pe + off[j]) = E[j];
+                for (int j = 0; j < NJ; j++) st_global_hint(reinterpret_cast<float4*>(pe + off[j]), E[j], keep);
                 if (lane < 16) pe[8 * D + lane] = Eml;
                 fence_acq_rel_gpu();
                 __syncwarp();
@@ -423,6 +426,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         // loop keeps running values (stage, parity, source address) instead of deriving them.
         uint32_t st = 0, empty_parity = 1;  // the next tile's stage; the parity its `empty` barrier is waited on with
         const bool one_copy = a.page_bytes == SM::tile_bytes;  // one tile per block: its values follow its keys
+        // Every KV byte is read once per launch: its lines leave the L2 first, so that what the launch
+        // keeps coming back to (partial results, records, queries) stays there.
+        const uint64_t stream_policy = l2_policy_evict_first();
         bool failed = false, queue_dry = false;
 #ifdef QVX_TRACE
         const uint32_t trace_base = 0; uint32_t tp = 0;
@@ -458,10 +464,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
                 mbar_expect_tx(fb, SM::stage_bytes);
                 if (one_copy) {
-                    bulk_g2s(dst, src, SM::stage_bytes, fb);
+                    bulk_g2s_hint(dst, src, SM::stage_bytes, fb, stream_policy);
                 } else {
-                    bulk_g2s(dst, src, SM::tile_bytes, fb);
-                    bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, fb);
+                    bulk_g2s_hint(dst, src, SM::tile_bytes, fb, stream_policy);
+                    bulk_g2s_hint(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, fb, stream_policy);
                 }
                 if (++st == SM::stages) { st = 0; empty_parity ^= 1u; }
                 if (++bj == a.tiles_per_block) {

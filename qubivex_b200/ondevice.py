@@ -1,8 +1,9 @@
 """The runtime's side of device attention: the part of `OnDevice::routed_moe`
 (crates/qubivex-runtime/src/discrete.rs:840-945) that owns the KV pool, plans the block
 tables, lists the host rows the device does not hold, offers the op to the device and records
-what the pool holds afterwards.  Projections, norms, RoPE and the MoE layer itself are the
-stages before and after this path and are not here.
+what the pool holds afterwards.  The projections and the MoE layer itself are the stages before and
+after this path and are not here; clip, Q/K norms and RoPE run on the device when the caller hands
+over the raw projections with a `prelude`.
 """
 from __future__ import annotations
 
@@ -57,10 +58,13 @@ class OnDevice:
     def new_mirror(self, epoch: int = 0) -> Mirror:
         return self.kv.mirror(epoch)
 
-    def attention(self, seqs: list[AttnSeq], layer: int, q, k_new, v_new, variant: int = ATTN_AUTO):
+    def attention(self, seqs: list[AttnSeq], layer: int, q, k_new, v_new, variant: int = ATTN_AUTO, prelude: dict | None = None):
         """The attention stage of one layer for one decode pass.  Returns the outputs
         [token][head][d], or None when declined (no pool, no memory, or no free block: the
-        caller runs attention on the host, discrete.rs:870-891)."""
+        caller runs attention on the host, discrete.rs:870-891).  With `prelude`
+        (rope=..., clip=..., qk_norm=..., eps=...: DeviceMoeAttention's fields) q, k_new and v_new are the
+        raw projections, and k_new / v_new (float32 arrays) come back clipped, normed and rotated for the
+        host cache."""
         if self.kv is None:
             return None
         buf = self.kv_buffer()
@@ -83,8 +87,13 @@ class OnDevice:
                 sync[r, kv_out:] = sq.host_v[:, int(p), :].reshape(-1)
             if len(plan.copy_src):
                 self.device.block_copy(buf, self.geo, plan.copy_src, plan.copy_dst)
-            out = self.device.paged_attention(buf, self.geo, self.heads, q, k_new, v_new, plan.pos, plan.blocks,
-                                              plan.table_at, sync, plan.sync_to, variant=variant)
+            if prelude is not None:
+                out = self.device.attention_stage(buf, self.geo, self.heads, q, k_new, v_new, prelude["rope"], plan.pos, plan.blocks,
+                                                  plan.table_at, clip=prelude.get("clip"), qk_norm=prelude.get("qk_norm"),
+                                                  eps=prelude.get("eps", 1e-6), sync=sync, sync_to=plan.sync_to, variant=variant)
+            else:
+                out = self.device.paged_attention(buf, self.geo, self.heads, q, k_new, v_new, plan.pos, plan.blocks,
+                                                  plan.table_at, sync, plan.sync_to, variant=variant)
             self.kv.commit(plan, mirrors, layer)
             self.routed += 1
             self.last_plan = plan

@@ -256,3 +256,56 @@ def test_c4_churn_compaction_then_attention(dev):
         sq.mirror.drop()
     assert od.kv.stats().free == blocks
     od.close()
+
+
+# ---- the prelude inside the runtime's loop --------------------------------------------------------
+def test_decode_steps_from_raw_projections_keep_the_host_cache_in_step(dev):
+    """Each pass hands the device the raw projections; clip, norms and RoPE run there and the new
+    rows come back for the host cache (sim.rs:325-357).  After a cache reset everything is synced
+    from that host cache again, so its rows must be exactly the device's."""
+    heads, kvh, d, B, blocks = 16, 2, 128, 16, 96
+    geo_d, geo_o = qd.geometry(B, kvh, d, qd.BF16), oracle.geometry(B, kvh, d, oracle.BF16)
+    rng = np.random.default_rng(77)
+    od = OnDevice(dev, geo_d, heads, blocks=blocks)
+    n_bytes = blocks * oracle.block_bytes(geo_o)
+    dev.write(od.kv_buffer(), 0, np.zeros(n_bytes, dtype=np.uint8))
+    pool_o = np.zeros(n_bytes, dtype=np.uint8)
+    seqs = [Seq(HostCache(kvh, d, 300, rng, scale=0.0)) for _ in range(3)]   # empty caches: everything comes from decode steps
+    norms = (rng.standard_normal(heads * d, dtype=np.float32), rng.standard_normal(kvh * d, dtype=np.float32))
+    clip, eps, theta = 3.0, 1e-5, 10000.0
+    inv = (1.0 / (np.float32(theta) ** (np.arange(0, d, 2, dtype=np.float32) / np.float32(d)))).astype(np.float32)
+
+    def rope_for(positions):
+        f = np.outer(np.asarray(positions, dtype=np.float32), inv).astype(np.float32)
+        return np.concatenate([np.cos(f), np.sin(f)], axis=1).astype(np.float32)
+
+    for step in range(40):
+        if step == 25:   # the host cache was cleared and refilled: a new epoch, the device re-syncs all rows
+            for sq in seqs:
+                sq.host.epoch += 1
+        s = len(seqs)
+        q = rng.standard_normal((s, heads * d), dtype=np.float32)
+        k = rng.standard_normal((s, kvh * d), dtype=np.float32) * 2
+        v = rng.standard_normal((s, kvh * d), dtype=np.float32) * 2
+        rope = rope_for([sq.host.len for sq in seqs])
+        wq, wk, wv = oracle.attn_prelude(q, k, v, heads, kvh, d, rope, clip=clip, qk_norm=norms, eps=eps)
+        aseqs = [sq.attn_seq() for sq in seqs]
+        k_back, v_back = k.copy(), v.copy()
+        out = od.attention(aseqs, 0, q, k_back, v_back, variant=qd.ATTN_SPLIT,
+                           prelude={"rope": rope, "clip": clip, "qk_norm": norms, "eps": eps})
+        assert out is not None
+        assert np.array_equal(k_back.view(np.uint32), wk.view(np.uint32)) and np.array_equal(v_back.view(np.uint32), wv.view(np.uint32))
+        for t, (sq, a) in enumerate(zip(seqs, aseqs)):
+            sq.mirror = a.mirror
+            sq.host.k[:, sq.host.len, :] = k_back[t].reshape(kvh, d)   # what the host cache keeps
+            sq.host.v[:, sq.host.len, :] = v_back[t].reshape(kvh, d)
+        want = oracle_step(pool_o, geo_o, heads, od.last_plan, seqs, wq, wk, wv)
+        if step == 25:
+            assert len(od.last_plan.sync_to) == 3 * 25
+        for sq in seqs:
+            sq.host.len += 1
+        ok, err = within(out, want, "bf16")
+        assert ok, (step, err)
+    for sq in seqs:
+        sq.mirror.drop()
+    od.close()
