@@ -72,8 +72,9 @@ struct TileStream {
             const uint8_t* src = base + (uint64_t)blk * block_bytes + (uint64_t)(tau % tiles_per_block) * tile_bytes;
             fence_proxy_async();
             mbar_expect_tx(bar, stage_bytes);
-            bulk_g2s(dst, src, tile_bytes, bar);
-            bulk_g2s(dst + tile_bytes, src + page_bytes, tile_bytes, bar);
+            const uint64_t stream_policy = l2_policy_evict_first();  // read once: leave the L2 to the partial results
+            bulk_g2s_hint(dst, src, tile_bytes, bar, stream_policy);
+            bulk_g2s_hint(dst + tile_bytes, src + page_bytes, tile_bytes, bar, stream_policy);
         }
     }
 };

@@ -102,8 +102,9 @@ __global__ void __launch_bounds__(STHREADS, 3) attn_static_kernel(StaticArgs a) 
             const uint8_t* src = base + (uint64_t)blk * a.block_bytes + (uint64_t)(tau % a.tiles_per_block) * SM::tile_bytes;
             fence_proxy_async();
             mbar_expect_tx(bar, SM::stage_bytes);
-            bulk_g2s(dst, src, SM::tile_bytes, bar);
-            bulk_g2s(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, bar);
+            const uint64_t stream_policy = l2_policy_evict_first();  // read once: leave the L2 to the partial results
+            bulk_g2s_hint(dst, src, SM::tile_bytes, bar, stream_policy);
+            bulk_g2s_hint(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, bar, stream_policy);
         }
     };
     const uint32_t pre = n_my < SM::stages ? n_my : SM::stages;

@@ -18,7 +18,9 @@ from pathlib import Path
 import numpy as np
 from safetensors.torch import load_file
 
-ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) != 2:
+    sys.exit("usage: python tests/golden/make_tiny_attention.py /path/to/qubivex")
+ref = Path(sys.argv[1])
 golden = json.loads((ref / "fixtures/oracle/forward.json").read_text())
 prompt = np.array(golden["prompt"], dtype=np.int64)
 out = {"prompt": prompt}
