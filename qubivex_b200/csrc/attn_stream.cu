@@ -109,7 +109,10 @@ struct StreamSmem {
     static constexpr uint32_t tile_bytes = TILE * D * 2;
     static constexpr uint32_t stage_bytes = 2 * tile_bytes;
     static constexpr uint32_t q_stride = D * 4 + 16;  // padded rows: fragment reads hit 32 distinct banks
-    static constexpr uint32_t res_floats = 16 + 8 * D;  // one warp's state: m[8], l[8], acc[8][D]
+    // One warp's state: m[8], l[8], acc[8][D] with rows of D + 4 floats: the lanes that hold heads 2t
+    // and positions g then store to 32 distinct banks.
+    static constexpr uint32_t res_row = D + 4;
+    static constexpr uint32_t res_floats = 16 + 8 * res_row;
     static constexpr uint32_t res_bytes = MAIL_SLOTS * CW * res_floats * 4;  // two items' worth: one being merged, one being filled
     static constexpr uint32_t q_bytes = Q_SLOTS * 8 * q_stride;
     static constexpr uint32_t rec_bytes = REC_SLOTS * REC_WORDS * 4;
@@ -628,7 +631,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 for (int c = 0; c < CW; c++) {
                     const float* r = rb + c * SM::res_floats;
                     const float wg = ex2(mc[c] - M);
-                    const float4 v = *reinterpret_cast<const float4*>(r + 16 + h * D + x);
+                    const float4 v = *reinterpret_cast<const float4*>(r + 16 + h * SM::res_row + x);
                     acc.x = fmaf(v.x, wg, acc.x); acc.y = fmaf(v.y, wg, acc.y);
                     acc.z = fmaf(v.z, wg, acc.z); acc.w = fmaf(v.w, wg, acc.w);
                     l = fmaf(r[8 + h], wg, l);
@@ -863,10 +866,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         }
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
-            res[16 + (2 * t) * D + 16 * mt + g] = o[mt][0];
-            res[16 + (2 * t + 1) * D + 16 * mt + g] = o[mt][1];
-            res[16 + (2 * t) * D + 16 * mt + g + 8] = o[mt][2];
-            res[16 + (2 * t + 1) * D + 16 * mt + g + 8] = o[mt][3];
+            res[16 + (2 * t) * SM::res_row + 16 * mt + g] = o[mt][0];
+            res[16 + (2 * t + 1) * SM::res_row + 16 * mt + g] = o[mt][1];
+            res[16 + (2 * t) * SM::res_row + 16 * mt + g + 8] = o[mt][2];
+            res[16 + (2 * t + 1) * SM::res_row + 16 * mt + g + 8] = o[mt][3];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(rfull0 + ms * 8);

@@ -424,3 +424,60 @@ def test_a_step_appended_inside_a_run_lands_in_the_pool(dev, monkeypatch):
         assert np.array_equal(got_pool, want_pool), run
         ok, err = within(got, want, "bf16")
         assert ok, (run, err)
+
+
+def test_hundreds_of_overlapping_launches_leave_no_trace_in_the_scratch(dev):
+    """240 launches back to back under programmatic dependent launch, each with more work items than
+    resident CTAs (queue, late claims, runs, folding ahead, both scratch halves all in play), against
+    the same launches one at a time: every output and the pool bit for bit, and a clean status."""
+    torch = pytest.importorskip("torch")
+    import ctypes as C
+    from qubivex_b200.device import ptr
+    heads, kvh, d, B, s, layers, steps = 32, 4, 128, 16, 96, 6, 40
+    geo = qd.geometry(B, kvh, d, qd.BF16)
+    bb = qd.block_bytes(geo)
+    rng = np.random.default_rng(191)
+    lengths = rng.integers(600, 3000, size=s)
+    nb = (lengths + steps + B - 1) // B
+    per_layer = int(nb.sum())
+    perm = rng.permutation(per_layer * layers).astype(np.uint32)
+    table_at = np.concatenate([[0], np.cumsum(nb)[:-1]]).astype(np.uint32)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    pool0 = (torch.randn(per_layer * layers * bb // 2, device="cuda", generator=g) * 0.3).to(torch.bfloat16)
+    q = [torch.randn((s, heads, d), device="cuda", generator=g) * 0.3 for _ in range(4)]
+    kn = [torch.randn((s, kvh * d), device="cuda", generator=g) * 0.3 for _ in range(4)]
+    vn = [torch.randn((s, kvh * d), device="cuda", generator=g) * 0.3 for _ in range(4)]
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    tabs = []
+    for t in range(steps):
+        pos = (lengths + t).astype(np.uint32)
+        for l in range(layers):
+            tb = C.c_void_p()
+            blocks = perm[l * per_layer:(l + 1) * per_layer].copy()
+            dev.check(dev.lib.qvx_tables_create(dev.h, C.byref(geo), per_layer * layers, heads, s, ptr(pos), ptr(blocks), per_layer,
+                                                ptr(table_at), C.byref(tb)))
+            tabs.append(tb)
+
+    def run(flag, sync_each):
+        pool = pool0.clone()
+        outs = torch.empty((steps * layers, s, heads, d), device="cuda")
+        i = 0
+        for t in range(steps):
+            for l in range(layers):
+                dev.check(dev.lib.qvx_kv_append_attn_decode(dev.h, tabs[i], ptr(pool), ptr(kn[t % 4]), ptr(vn[t % 4]), ptr(q[t % 4]),
+                                                            ptr(outs[i]), qd.ATTN_SPLIT | flag, stream))
+                if sync_each:
+                    torch.cuda.synchronize()
+                i += 1
+        torch.cuda.synchronize()
+        dev.kernel_times()   # drains the timing events; raises if a kernel reported a status
+        return outs, pool
+
+    want_out, want_pool = run(0, True)
+    for _ in range(2):
+        got_out, got_pool = run(qd.ATTN_POOL_SETTLED, False)
+        assert torch.equal(got_pool.view(torch.int16), want_pool.view(torch.int16))
+        assert torch.equal(got_out.view(torch.int32), want_out.view(torch.int32))
+    assert bool(torch.isfinite(want_out).all())
+    for tb in tabs:
+        dev.lib.qvx_tables_free(tb)
