@@ -181,7 +181,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     W, K = args.warmup, args.steps
     We, Ke = min(W, 3), K
     total_steps = W + K + We + Ke
-    lengths = wl.contexts(shape, SEED + rank)            # positions prefilled per sequence
+    # Every rank draws the same context lengths (so every GPU has the same number of bytes to move and
+    # the max over ranks measures the machines, not the luck of the draw); its values and its block
+    # placement are its own.
+    lengths = wl.contexts(shape, SEED)                   # positions prefilled per sequence
     nb_seq = (lengths + total_steps + B - 1) // B          # table entries per sequence, with room to grow
     blocks_per_layer = int(nb_seq.sum())
     pool_blocks = blocks_per_layer * layers
