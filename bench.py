@@ -71,7 +71,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -79,52 +79,64 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.perf_counter(), [x.strip() for x in line.split(",")]))
 
-    def stop(self) -> dict:
+    def stop(self, t_from: float, t_to: float) -> dict:
+        """Samples read between t_from and t_to (perf_counter: the device was under load then); all of
+        them if the interval was too short to catch one."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
         self.proc.terminate()
-        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        inside = [r for t, r in self.rows if t_from <= t <= t_to]
+        rows = inside or [r for _, r in self.rows]
+        sm = [float(r[0]) for r in rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in rows)]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "samples_under_load": len(inside)}
 
 
 # ---------------------------------------------------------------------------------------------
-def cpu_sample(shape: wl.Shape, lengths: np.ndarray, threads: int, target_s: float, seed: int):
-    """Times the CPU restatement of the reference's path (one task per (token, head) reading the
-    paged pool, as its host path does) on a sample: `n` sequences x 1 layer x 1 decode step,
-    repeated until about `target_s` of wall time.  Returns (seconds per sequence-layer, text)."""
-    import oracle
+class CpuSample:
+    """The CPU restatement of the reference's path (one task per (token, head) reading the paged
+    pool, as its host path does) on a sample of the workload: `n` sequences x 1 layer x 1 decode
+    step.  The pool is made once, for the longest contexts the run will ask for."""
 
-    n = min(len(lengths), 16)
-    lens = np.asarray(lengths[:n], dtype=np.int64) + 1
-    geo = oracle.geometry(shape.block_tokens, shape.kv_heads, shape.head_dim, oracle.BF16, oracle.LAYOUT_NATIVE)
-    bb = oracle.block_bytes(geo)
-    nb = int(((lens + shape.block_tokens - 1) // shape.block_tokens).sum())
-    rng = np.random.default_rng([seed, 0x77])
-    perm = rng.permutation(nb + 8).astype(np.uint32)
-    tabs = wl.tables_for(lens, shape.block_tokens, perm)
-    scale = wl.value_scale(shape)
-    pool = oracle.narrow(wl.normal(rng, ((nb + 8) * bb // 2,), scale), oracle.BF16).view(np.uint8)
-    q = wl.normal(rng, (n, shape.heads, shape.head_dim), scale)
-    oracle.attn_decode(pool, geo, shape.heads, q[:1], tabs.pos[:1], tabs.blocks, tabs.table_at[:1], threads=threads)  # warm
-    reps, t0 = 0, time.perf_counter()
-    while True:
-        rc, _ = oracle.attn_decode(pool, geo, shape.heads, q, tabs.pos, tabs.blocks, tabs.table_at, threads=threads)
-        assert rc == 0
-        reps += 1
-        dt = time.perf_counter() - t0
-        if dt >= target_s or reps >= 64:
-            break
-    per_seq_layer = dt / (reps * n)
-    text = (f"{n} sequences (contexts {int(lens.min())}-{int(lens.max())}) x 1 layer x 1 decode step, repeated {reps}x "
-            f"({dt:.1f} s); tokens/s = 1 / ({shape.layers} layers x seconds per sequence-layer)")
-    return per_seq_layer, text
+    def __init__(self, shape: wl.Shape, lengths: np.ndarray, grow: int, threads: int, seed: int):
+        import oracle
+
+        self.oracle, self.shape, self.threads = oracle, shape, threads
+        self.n = min(len(lengths), 16)
+        self.base = np.asarray(lengths[:self.n], dtype=np.int64)
+        B = shape.block_tokens
+        self.geo = oracle.geometry(B, shape.kv_heads, shape.head_dim, oracle.BF16, oracle.LAYOUT_NATIVE)
+        nb = int(((self.base + grow + 1 + B - 1) // B).sum())
+        self.rng = np.random.default_rng([seed, 0x77])
+        self.perm = self.rng.permutation(nb + 8).astype(np.uint32)
+        scale = wl.value_scale(shape)
+        self.pool = oracle.narrow(wl.normal(self.rng, ((nb + 8) * oracle.block_bytes(self.geo) // 2,), scale), oracle.BF16).view(np.uint8)
+        self.q = wl.normal(self.rng, (self.n, shape.heads, shape.head_dim), scale)
+        tabs = wl.tables_for(self.base + 1, B, self.perm)
+        oracle.attn_decode(self.pool, self.geo, shape.heads, self.q[:1], tabs.pos[:1], tabs.blocks, tabs.table_at[:1], threads=threads)  # warm
+
+    def run(self, step: int, target_s: float):
+        """Contexts `step` positions on; repeated until about `target_s` of wall time.  Returns (seconds per
+        sequence-layer, text)."""
+        lens = self.base + step + 1
+        tabs = wl.tables_for(lens, self.shape.block_tokens, self.perm)
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            rc, _ = self.oracle.attn_decode(self.pool, self.geo, self.shape.heads, self.q, tabs.pos, tabs.blocks, tabs.table_at,
+                                            threads=self.threads)
+            assert rc == 0
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt >= target_s or reps >= 64:
+                break
+        text = (f"{self.n} sequences (contexts {int(lens.min())}-{int(lens.max())}) x 1 layer x 1 decode step, repeated {reps}x "
+                f"({dt:.1f} s); tokens/s = 1 / ({self.shape.layers} layers x seconds per sequence-layer)")
+        return dt / (reps * self.n), text
 
 
 def run_reference(args, rank: int, world: int) -> None:
@@ -136,8 +148,10 @@ def run_reference(args, rank: int, world: int) -> None:
     lengths = wl.contexts(shape, SEED)
     threads = os.cpu_count() or 1
     per = []
-    for i in range(args.warmup + args.steps):
-        sec, text = cpu_sample(shape, lengths + i, threads, target_s=max(2.0, 20.0 / max(args.steps, 1)), seed=SEED + i)
+    total = args.warmup + args.steps
+    sample = CpuSample(shape, lengths, total, threads, SEED)
+    for i in range(total):
+        sec, text = sample.run(i, target_s=max(0.5, 60.0 / max(total, 1)))  # the whole run: about a minute of timed work
         if i >= args.warmup:
             per.append(sec)
     sec = float(np.mean(per))
@@ -169,6 +183,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    sampler = ClockSampler(local_rank)  # runs from here on (its start-up takes longer than a short timed region)
+    sampler.start()
     dev = qd.CudaDevice(local_rank, timing=4)  # CUDA events around every 4th launch of each kernel
     lib = dev.lib
     shape = wl.C2
@@ -248,15 +264,14 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         step(t)
     barrier()
     dev.reset_kernel_times()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_load0 = time.perf_counter()
     e0.record()
     for t in range(W, W + K):
         step(t)
     e1.record()
     barrier()
-    clocks = sampler.stop()
+    clocks = sampler.stop(t_load0, time.perf_counter())
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     if dist is not None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -339,7 +354,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu:
-        sec, text = cpu_sample(shape, lengths + W + K, os.cpu_count() or 1, target_s=12.0, seed=SEED)
+        sec, text = CpuSample(shape, lengths, W + K, os.cpu_count() or 1, SEED).run(W + K, target_s=12.0)
         line["cpu_baseline"] = {"value": 1.0 / (layers * sec), "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": text}
     else:
         line["cpu_baseline"] = None
@@ -355,7 +370,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 48 (debugging only)")
