@@ -132,7 +132,7 @@ class CpuSample:
             assert rc == 0
             reps += 1
             dt = time.perf_counter() - t0
-            if dt >= target_s or reps >= 64:
+            if dt >= target_s or reps >= 4096:
                 break
         text = (f"{self.n} sequences (contexts {int(lens.min())}-{int(lens.max())}) x 1 layer x 1 decode step, repeated {reps}x "
                 f"({dt:.1f} s); tokens/s = 1 / ({self.shape.layers} layers x seconds per sequence-layer)")
