@@ -281,10 +281,13 @@ static uint32_t chunk_tokens_for(const Layout& L, uint32_t len) {
 // less often; with few, items stay single chunks and the queue evens the CTAs out.  A run never
 // exceeds RUN_TOKENS positions (its block ids ride in the item's record).
 static const uint32_t RUN_TOKENS = 2048;
-static uint32_t run_chunks_for(size_t total_chunks, uint32_t resident_ctas) {
+static uint32_t run_chunks_override() {
     const char* v = getenv("QVX_RUN_CHUNKS");  // experiments and tests: a fixed run length (read at every op)
-    const long configured = v ? atol(v) : 0;
-    if (configured > 0) return (uint32_t)configured;
+    const long n = v ? atol(v) : 0;
+    return n > 0 ? (uint32_t)n : 0u;
+}
+static uint32_t run_chunks_for(size_t total_chunks, uint32_t resident_ctas) {
+    if (const uint32_t configured = run_chunks_override()) return configured;
     const size_t per_cta = total_chunks / std::max(1u, resident_ctas);
     return (uint32_t)std::min<size_t>(4, std::max<size_t>(1, per_cta / 6));
 }
@@ -329,15 +332,19 @@ struct PlanCache {
     uint32_t B = 0, kvh = 0, d = 0, dtype = 0, layout = 0;
     size_t heads = 0, s = 0;
     bool split = false;
-    uint32_t ctas = 0;
+    uint32_t ctas = 0, knobs = 0;
     std::vector<uint32_t> pos;
     TableImage im{};                       // counts and sizes; the offsets depend on n_blocks and are redone
     std::vector<qvx_item_header> headers;  // in launch order
     std::vector<uint32_t> seq_off, count;  // per item: first block's offset in its sequence's table, blocks
 };
 
+static uint32_t run_tail_chunks();
+// What the environment says about runs right now: a kept work list made under other settings is not reused.
+static uint32_t run_knobs() { return run_chunks_override() * 65536u + run_tail_chunks(); }
+
 static bool plan_hit(const PlanCache* c, const Layout& L, size_t heads, size_t s, const uint32_t* pos, bool split, uint32_t ctas) {
-    return c && c->valid && c->B == L.B && c->kvh == L.kvh && c->d == L.d && c->dtype == L.dtype && c->layout == L.layout &&
+    return c && c->valid && c->knobs == run_knobs() && c->B == L.B && c->kvh == L.kvh && c->d == L.d && c->dtype == L.dtype && c->layout == L.layout &&
            c->heads == heads && c->s == s && c->split == split && c->ctas == ctas && memcmp(c->pos.data(), pos, 4 * s) == 0;
 }
 
@@ -434,7 +441,7 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     }
     if (cache) {
         cache->B = L.B; cache->kvh = L.kvh; cache->d = L.d; cache->dtype = L.dtype; cache->layout = L.layout;
-        cache->heads = heads; cache->s = s; cache->split = split; cache->ctas = ctas;
+        cache->heads = heads; cache->s = s; cache->split = split; cache->ctas = ctas; cache->knobs = run_knobs();
         cache->pos.assign(pos, pos + s);
         cache->im = im;
         cache->headers.resize(im.n_items); cache->seq_off.resize(im.n_items); cache->count.resize(im.n_items);

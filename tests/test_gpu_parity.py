@@ -125,7 +125,8 @@ def test_split_attention_is_within_tolerance(dev, dtype, heads, kvh, d, B):
 def test_long_contexts_take_larger_chunks_and_a_merge_tree(dev):
     # 20000 positions: 1024-position chunks; 40000 and 70000: 2048-position chunks, the last
     # with more than 32 of them (two levels of the fan-in-8 merge tree).
-    c = Case(8, 1, 128, 16, "bf16", [20000, 40000, 70000, 513], seed=35, amp_qk=0.3)
+    # 4200 and 8705: 9 and 18 chunks of 512, i.e. merge nodes of 8 + 1 and 8 + 8 + 2 entries.
+    c = Case(8, 1, 128, 16, "bf16", [20000, 40000, 70000, 513, 4200, 8705], seed=35, amp_qk=0.3)
     _, want = c.run_oracle()
     _, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
     ok, err = within(got, want, "bf16")
