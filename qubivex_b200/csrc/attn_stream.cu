@@ -61,6 +61,10 @@ constexpr int REC_SLOTS = 4;
 #ifndef QVX_FETCH_AHEAD
 #define QVX_FETCH_AHEAD (QVX_CLAIM_AHEAD / 2)
 #endif
+#ifndef QVX_ISSUE_LANES
+#define QVX_ISSUE_LANES 2
+#endif
+constexpr uint32_t ISSUE_LANES = QVX_ISSUE_LANES;  // lanes of the producer warp that issue tiles side by side
 constexpr uint32_t CLAIM_AHEAD = QVX_CLAIM_AHEAD;  // tiles before an item's end at which the producer claims the next item
 constexpr uint32_t FETCH_AHEAD = QVX_FETCH_AHEAD;  // ... and at which it asks for the item's record
 constexpr int REC_WORDS = 144;                 // header + up to 136 block ids
@@ -104,7 +108,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 template <int D>
 struct StreamSmem {
-    static constexpr int ctas_per_sm = D <= 128 ? 2 : 1;
+    static constexpr int ctas_per_sm = (D <= 128 && CW <= 4) ? 2 : 1;
     static constexpr uint32_t budget = (227u * 1024u) / ctas_per_sm - 1024u;
     static constexpr uint32_t tile_bytes = TILE * D * 2;
     static constexpr uint32_t stage_bytes = 2 * tile_bytes;
@@ -137,7 +141,9 @@ struct StreamSmem {
     static constexpr uint32_t abort_off = bar_off + n_bars * 8;
     static constexpr uint32_t mail_off = abort_off + 16;
     static constexpr uint32_t total = mail_off + NOTE_SLOTS * 32;
+#if QVX_CW <= 4  // (experiment builds with more consumer warps only run the head sizes that fit)
     static_assert(stages >= CW, "the ring needs a stage per consumer warp");
+#endif
 };
 
 // What the consumers tell the epilogue warp about an item when they start it, long before its
@@ -425,10 +431,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 mbar_arrive(recbar0 + slot * 8);
             }
         };
-        // Lane 0 issues every tile, one after the other, and nothing hides what each costs it: the
-        // loop keeps running values (stage, parity, source address) instead of deriving them.
-        uint32_t st = 0, empty_parity = 1;  // the next tile's stage; the parity its `empty` barrier is waited on with
+        // What one lane pays per tile -- an mbarrier wait, an expect-tx, the bulk copy, each a round
+        // through the shared-memory pipe -- is about 0.3 us, close to the 0.34 us a tile takes at the
+        // memory's rate: one lane alone can barely keep the ring full and never catches up after a
+        // pause.  So ISSUE_LANES lanes issue consecutive tiles in step (one instruction stream, a tile
+        // each); everything per tile is derived with shifts and constants, nothing with a division.
+        uint32_t nprod = 0;  // tiles issued before the current item, over all items
         const bool one_copy = a.page_bytes == SM::tile_bytes;  // one tile per block: its values follow its keys
+        const uint32_t tpb = a.tiles_per_block;
+        const bool tpb_pow2 = (tpb & (tpb - 1u)) == 0u;
+        const uint32_t tpb_shift = 31u - (uint32_t)__clz((int)tpb);
         // Every KV byte is read once per launch: its lines leave the L2 first, so that what the launch
         // keeps coming back to (partial results, records, queries) stays there.
         const uint64_t stream_policy = l2_policy_evict_first();
@@ -458,12 +470,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             const uint8_t* base = a.pool + (uint64_t)kvh * 2u * a.page_bytes;
             const uint32_t ntiles = (tokens + TILE - 1) / TILE;
             const uint32_t* ids = rec + QVX_ITEM_HEADER_WORDS;
-            const uint32_t nblk = (ntiles + a.tiles_per_block - 1) / a.tiles_per_block;
-            uint32_t bi = 0, bj = 0;  // the next tile: block of the item, tile of the block
-            const uint8_t* src = base + (uint64_t)ids[0] * a.block_bytes;
-            auto issue_tile = [&]() -> bool {  // lane 0 only: the item's next tile
+            auto issue_tile = [&](uint32_t tau) -> bool {  // any lane: tile `tau` of this item
+                const uint32_t n = nprod + tau;
+                const uint32_t st = n % SM::stages, parity = ((n / SM::stages) & 1u) ^ 1u;
                 const uint32_t eb = empty0 + st * 8, fb = full0 + st * 8;
-                if (!mbar_try_wait(eb, empty_parity) && !mbar_wait(eb, empty_parity)) return false;
+                if (!mbar_try_wait(eb, parity) && !mbar_wait(eb, parity)) return false;
+                const uint32_t bi = tpb_pow2 ? tau >> tpb_shift : tau / tpb, bj = tau - bi * tpb;
+                const uint8_t* src = base + (uint64_t)ids[bi] * a.block_bytes + bj * SM::tile_bytes;
                 const uint32_t dst = sbase + SM::ring_off + st * SM::stage_bytes;
                 mbar_expect_tx(fb, SM::stage_bytes);
                 if (one_copy) {
@@ -472,13 +485,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     bulk_g2s_hint(dst, src, SM::tile_bytes, fb, stream_policy);
                     bulk_g2s_hint(dst + SM::tile_bytes, src + a.page_bytes, SM::tile_bytes, fb, stream_policy);
                 }
-                if (++st == SM::stages) { st = 0; empty_parity ^= 1u; }
-                if (++bj == a.tiles_per_block) {
-                    bj = 0;
-                    if (++bi < nblk) src = base + (uint64_t)ids[bi] * a.block_bytes;
-                } else {
-                    src += SM::tile_bytes;
-                }
                 return true;
             };
             const bool last_chunk = rec[4] == NO_PART || rec[4] - rec[5] + rec[9] == rec[6];  // the run ends the sequence
@@ -486,10 +492,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             if (k == 0 && a.overlap) {
                 // The first item's old positions stream while the stream's earlier work finishes;
                 // a chunk that holds the step's new row waits, since its rows come from that work.
-                if (lane == 0 && !(last_chunk && a.k_new != nullptr)) {
-                    const uint32_t pre = ntiles < SM::stages ? ntiles : SM::stages;
-                    for (; tau0 < pre; tau0++)
-                        if (!issue_tile()) { failed = true; break; }
+                if (!(last_chunk && a.k_new != nullptr)) {
+                    tau0 = ntiles < SM::stages ? ntiles : SM::stages;
+                    if (lane < ISSUE_LANES)
+                        for (uint32_t tau = lane; tau < tau0; tau += ISSUE_LANES)
+                            if (!issue_tile(tau)) { failed = true; break; }
                 }
                 grid_dep_wait();
             }
@@ -526,9 +533,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 bulk_g2s(sbase + SM::q_off + (qslot * 8 + lane) * SM::q_stride, a.q + ((size_t)seq * a.heads + head0 + lane) * D, D * 4,
                          qfull0 + qslot * 8);
             }
-            if (lane == 0) {
+            if (lane < ISSUE_LANES) {
 #ifdef QVX_TRACE
-                TRACE(tp, 2);  // item issue begins
+                if (lane == 0) TRACE(tp, 2);  // item issue begins
 #endif
                 // Item k + 1 is claimed late: CLAIM_AHEAD tiles before this item's last tile is
                 // asked for, which is about the time its index and then its record take to come
@@ -549,19 +556,23 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     queue_dry = idx_next >= a.n_items;
                     fetched = true;
                 };
-                for (uint32_t tau = tau0; tau < ntiles && !failed; tau++) {
-                    if (tau == claim_at && !queue_dry) { claimed = atomicAdd(a.queue, 1u); asked = true; }
-                    if (tau == fetch_at) fetch_next();
-                    if (!issue_tile()) failed = true;
+                for (uint32_t t0 = tau0; t0 < ntiles && !failed; t0 += ISSUE_LANES) {
+                    if (lane == 0) {  // the queue is lane 0's business
+                        if (!asked && !queue_dry && t0 + ISSUE_LANES > claim_at) { claimed = atomicAdd(a.queue, 1u); asked = true; }
+                        if (!fetched && t0 + ISSUE_LANES > fetch_at) fetch_next();
+                    }
+                    const uint32_t tau = t0 + lane;
+                    if (tau < ntiles && !issue_tile(tau)) failed = true;
                 }
-                if (!fetched && !failed) {  // every tile went out before the dependency wait
+                if (lane == 0 && !fetched && !failed) {  // every tile went out before the dependency wait
                     if (!queue_dry) { claimed = atomicAdd(a.queue, 1u); asked = true; }
                     fetch_next();
                 }
 #ifdef QVX_TRACE
-                TRACE(tp, 3);  // item issue ends
+                if (lane == 0) TRACE(tp, 3);  // item issue ends
 #endif
             }
+            nprod += ntiles;
             if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
         }
         if (lane == 0) {
