@@ -46,7 +46,7 @@ UNIT = "tokens/s"
 SEED = 20261125
 # dram__bytes_read.sum + dram__bytes_write.sum of one attention launch over its algorithmic
 # bytes, from the ncu capture summarised in profiles/ (one layer of this workload).
-DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.013
+DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.012
 
 
 def env_int(name: str, default: int) -> int:
