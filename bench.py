@@ -303,6 +303,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     p_q, p_k, p_v, p_ta, p_geo = ptr(qh), ptr(kh), ptr(vh), ptr(table_at), C.byref(geo)
     p_blocks, p_out = [ptr(b) for b in layer_blocks], [ptr(o) for o in oh]
     host_call = lib.qvx_paged_attention_host_async
+    # consecutive ops serve different layers (disjoint blocks): they may overlap each other's ends
+    host_variant = qd.ATTN_AUTO | (qd.ATTN_POOL_SETTLED if layers >= 2 else 0)
 
     def step_host(t: int):
         nonlocal h2d, d2h
@@ -310,7 +312,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         p_pos = ptr(pos)
         for l in range(layers):
             rc = host_call(dev.h, pool.handle, p_geo, heads, s, p_q, p_k, p_v, p_pos, p_blocks[l], blocks_per_layer, p_ta, None, None, 0,
-                           p_out[l], qd.ATTN_AUTO)
+                           p_out[l], host_variant)
             if rc:
                 dev.check(rc)
         dev.wait()

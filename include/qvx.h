@@ -169,6 +169,9 @@ const uint32_t *qvx_tables_table_at(qvx_tables *t);
  * launch, starts streaming the old positions while the launch before it drains, and waits
  * (griddepcontrol.wait) before it reads q, k_new or v_new or writes anything. */
 #define QVX_ATTN_POOL_SETTLED 0x100
+/* On the host-memory calls (qvx_paged_attention_host_async) the same flag says: no op still in flight
+ * on this device writes the blocks this op reads or writes.  Ops so marked (with no sync rows) may run
+ * their kernels side by side with the previous op's; an op without it waits for every op before it. */
 
 /* Paged decode attention: `attn_decode.comp` (shaders/attn_decode.comp:60-175), the gather
  * and `attend` of sim.rs:400-429.  q, out: s x heads x head_dim f32, [token][head][d].

@@ -90,6 +90,8 @@ struct DeviceExtras {
     int* status_host = nullptr;
     int* status_dev = nullptr;
     cudaStream_t h2d = nullptr, d2h = nullptr;
+    cudaStream_t kernels2 = nullptr;       // the second kernel stream of independent host ops (see paged_attention_submit)
+    cudaEvent_t last_kernels[2] = {nullptr, nullptr};  // kernels_done of the last op on each kernel stream
     std::vector<cudaEvent_t> sync_events;  // spare events, handed to ops and taken back
     std::deque<HostOp> ops;                // oldest first
     size_t ring_head = 0;                  // where the next op's slice starts
@@ -196,7 +198,9 @@ static int32_t wait_locked(qvx_device* dev) {
     DeviceExtras* x = extras(dev);
     cudaError_t e = cudaStreamSynchronize(x->h2d);
     if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(x->kernels2);
     if (e == cudaSuccess) e = cudaStreamSynchronize(x->d2h);
+    x->last_kernels[0] = x->last_kernels[1] = nullptr;
     dev->xfer.wait_ns += now_ns() - t0;
     dev->xfer.fence_waits++;
     for (HostOp& op : x->ops) retire(dev, x, op);
@@ -609,6 +613,7 @@ int32_t qvx_open(const qvx_config* cfg, qvx_device** out) {
     e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&x->h2d, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&x->d2h, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&x->kernels2, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaHostAlloc((void**)&x->status_host, sizeof(int), cudaHostAllocMapped);
     if (e == cudaSuccess) {
         *x->status_host = 0;
@@ -653,7 +658,7 @@ void qvx_close(qvx_device* dev) {
     }
     if (x) {
         for (cudaEvent_t ev : x->sync_events) cudaEventDestroy(ev);
-        cudaStreamDestroy(x->h2d); cudaStreamDestroy(x->d2h);
+        cudaStreamDestroy(x->h2d); cudaStreamDestroy(x->d2h); cudaStreamDestroy(x->kernels2);
         cudaFreeHost(x->status_host);
         delete x;
     }
@@ -915,7 +920,12 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
 
     const size_t kv_out = (size_t)L.kvh * L.d, q_out = heads * L.d;
     const bool split = attn_split_supported(L, heads) && (variant & 0xffu) != QVX_ATTN_EXACT;
-    variant &= 0xffu;  // the host op orders its own copies and kernels: no overlap with what precedes it
+    // QVX_ATTN_POOL_SETTLED on a host op: the caller's word that no op still in flight writes the blocks
+    // this op reads or writes (the ops of one decode step serve different layers).  Such ops alternate
+    // between two kernel streams, each tied to one half of the scratch, so that an op's kernel fills
+    // the SMs the previous op's kernel leaves at its end; an op without the flag waits for both.
+    const bool independent = (variant & QVX_ATTN_POOL_SETTLED) != 0 && split && n_sync == 0 && s > 0;
+    variant &= 0xffu;  // (the streams give the overlap: no programmatic dependent launch here)
     if (!dev->plan_cache) dev->plan_cache = new PlanCache;
     PlanCache* cache = static_cast<PlanCache*>(dev->plan_cache);
     const uint32_t ctas = stream_ctas(dev, L, heads);
@@ -960,7 +970,11 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
         if (rc) return rc;
     }
 
-    cudaStream_t h2d = x->h2d, cs = dev->stream, d2h = x->d2h;
+    // The scratch half the attention launch will take decides the stream: every user of a half is on
+    // the same stream, so two launches never share a half at the same time.
+    const uint32_t lane = split ? (dev->scratch_half & 1u) : 0u;
+    cudaStream_t h2d = x->h2d, cs = lane ? x->kernels2 : dev->stream, d2h = x->d2h;
+    if (!independent && x->last_kernels[lane ^ 1u]) cudaStreamWaitEvent(cs, x->last_kernels[lane ^ 1u], 0);
     cudaError_t e = cudaMemcpyAsync(ds + o_img, hs + o_img, im.bytes + up(4 * n_sync), cudaMemcpyHostToDevice, h2d);
     size_t in_bytes = im.bytes + 4 * n_sync;
     auto copy_in = [&](size_t off, const void* src, size_t bytes) {
@@ -996,6 +1010,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
                            (const float*)(ds + o_k), (const float*)(ds + o_v));
     if (rc) return rc;
     cudaEventRecord(op.kernels_done, cs);
+    x->last_kernels[lane] = op.kernels_done;
     cudaStreamWaitEvent(d2h, op.kernels_done, 0);
     if (s) {
         e = cudaMemcpyAsync(out, ds + o_out, 4 * s * q_out, cudaMemcpyDeviceToHost, d2h);

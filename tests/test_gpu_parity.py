@@ -482,3 +482,32 @@ def test_hundreds_of_overlapping_launches_leave_no_trace_in_the_scratch(dev):
     assert bool(torch.isfinite(want_out).all())
     for tb in tabs:
         dev.lib.qvx_tables_free(tb)
+
+
+def test_independent_host_ops_side_by_side_give_the_same_bits(dev):
+    # Host ops marked QVX_ATTN_POOL_SETTLED (each on its own pool here, as layers are) alternate between
+    # two kernel streams; the same ops one at a time, unmarked, are the reference.  An unmarked op in
+    # the middle must still see everything before it.
+    cases = [Case(32, 4, 128, 16, "bf16", [900 + 37 * i, 300, 2047 - 11 * i, 1200], seed=120 + i) for i in range(6)]
+    bufs = []
+    try:
+        for c in cases:
+            b = dev.alloc(c.pool_blocks * c.bb)
+            dev.write(b, 0, c.host_pool())
+            bufs.append(b)
+        # prefill through one unmarked synchronous op per pool (sync rows + the new row)
+        want = [dev.paged_attention(b, c.geo_d, c.heads, c.q, c.k_new, c.v_new, c.pos, c.blocks, c.table_at, c.sync, c.sync_to,
+                                    variant=qd.ATTN_SPLIT) for b, c in zip(bufs, cases)]
+        outs = [[np.empty_like(w) for w in want] for _ in range(4)]
+        for r in range(4):
+            for i, (b, c) in enumerate(zip(bufs, cases)):
+                flag = 0 if (r == 2 and i == 3) else qd.ATTN_POOL_SETTLED
+                dev.paged_attention(b, c.geo_d, c.heads, c.q, c.k_new, c.v_new, c.pos, c.blocks, c.table_at, out=outs[r][i],
+                                    variant=qd.ATTN_SPLIT | flag, wait=False)
+        dev.wait()
+        for r in range(4):
+            for i in range(len(cases)):
+                assert np.array_equal(outs[r][i].view(np.uint32), want[i].view(np.uint32)), (r, i)
+    finally:
+        for b in bufs:
+            b.free()
