@@ -41,13 +41,17 @@ __device__ __forceinline__ bool row_target(const RowArgs& a, uint32_t r, uint32_
     return true;
 }
 
-// grid: ceil(n * kvh * 2 * chunks_per_row / 256) x 256 threads.
+// grid: (ceil(NATIVE_GROUP * kvh * 2 * chunks_per_row / 256), ceil(n / NATIVE_GROUP)) x 256 threads:
+// blockIdx.y picks a group of NATIVE_GROUP rows, so a thread's index inside the group fits 32 bits
+// and is split with 32-bit divisions.
+constexpr uint32_t NATIVE_GROUP = 1024;
 __global__ void __launch_bounds__(256) kv_rows_native_kernel(RowArgs a) {
     const uint32_t cpr = a.L.row_bytes >> 4;  // chunks per row
     const uint32_t per_row = a.L.kvh * 2u * cpr;
-    uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (uint64_t)a.n * per_row) return;
-    uint32_t r = (uint32_t)(idx / per_row), w = (uint32_t)(idx % per_row);
+    const uint32_t row0 = blockIdx.y * NATIVE_GROUP, rows = min(NATIVE_GROUP, a.n - row0);
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * per_row) return;
+    uint32_t r = row0 + idx / per_row, w = idx % per_row;
     uint32_t g = w / (2u * cpr), kv = (w / cpr) & 1u, c = w % cpr;
     uint32_t block, slot;
     if (!row_target(a, r, block, slot)) return;
@@ -96,8 +100,10 @@ int32_t launch_kv_rows(qvx_device* dev, const Layout& L, void* pool, const float
     bool aligned = (((uintptr_t)k_rows | (uintptr_t)v_rows | (uintptr_t)pool) & 15u) == 0 &&
                    (row_stride_f32 * 4) % 16 == 0;
     if (L.layout == QVX_LAYOUT_NATIVE && aligned) {
-        uint64_t total = (uint64_t)n * L.kvh * 2u * (L.row_bytes >> 4);
-        kv_rows_native_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
+        const uint32_t per_row = L.kvh * 2u * (L.row_bytes >> 4);
+        const uint32_t rows_x = (uint32_t)std::min<size_t>(n, NATIVE_GROUP);
+        dim3 grid((rows_x * per_row + 255u) / 256u, (unsigned)((n + NATIVE_GROUP - 1) / NATIVE_GROUP));
+        kv_rows_native_kernel<<<grid, 256, 0, s>>>(a);
     } else {
         uint64_t total = (uint64_t)n * 2u * L.kvh * L.d;
         kv_rows_element_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(a);
