@@ -469,6 +469,11 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
                 keys.push_back(Key{std::min(len, (c + r) * chunk) - c * chunk, (uint32_t)t, grp, c, r});
             });
     }
+    // Among items of equal size the early chunks of every sequence go first, then the next chunks of
+    // every sequence, and so on: the chunks of one merge node then arrive rounds apart, not together,
+    // so its last arrival finds the others long published (and folds them while it streams) instead of
+    // eight CTAs finishing a node's chunks at once and one of them waiting for seven publications.
+    std::stable_sort(keys.begin(), keys.end(), [](const Key& a, const Key& b) { return a.c < b.c; });
     // (a counting sort: tokens <= max_chunk, and this runs once per op on the host's critical path)
     std::vector<uint32_t> start(max_chunk + 2, 0);
     for (const Key& k : keys) start[max_chunk - k.tokens + 1]++;
