@@ -514,10 +514,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                         const float* src = (kv ? a.v_new : a.k_new) + (size_t)seq * a.kv_out + kvh * D + c * 8;
                         const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
                         uint4 w;
-                        w.x = (uint32_t)narrow16(lo.x, DT) | ((uint32_t)narrow16(lo.y, DT) << 16);
-                        w.y = (uint32_t)narrow16(lo.z, DT) | ((uint32_t)narrow16(lo.w, DT) << 16);
-                        w.z = (uint32_t)narrow16(hi.x, DT) | ((uint32_t)narrow16(hi.y, DT) << 16);
-                        w.w = (uint32_t)narrow16(hi.z, DT) | ((uint32_t)narrow16(hi.w, DT) << 16);
+                        w.x = narrow16x2(lo.x, lo.y, DT);
+                        w.y = narrow16x2(lo.z, lo.w, DT);
+                        w.z = narrow16x2(hi.x, hi.y, DT);
+                        w.w = narrow16x2(hi.z, hi.w, DT);
                         *reinterpret_cast<uint4*>(row + (uint64_t)kv * a.page_bytes + ((c ^ (slot & 7u)) << 4)) = w;
                     }
                     __threadfence();  // the rows are in device memory ...

@@ -45,33 +45,60 @@ __device__ __forceinline__ bool row_target(const RowArgs& a, uint32_t r, uint32_
 // blockIdx.y picks a group of NATIVE_GROUP rows, so a thread's index inside the group fits 32 bits
 // and is split with 32-bit divisions.
 constexpr uint32_t NATIVE_GROUP = 1024;
+constexpr uint32_t NATIVE_PER_THREAD = 2;  // chunks per thread: all their loads are issued before anything waits
 __global__ void __launch_bounds__(256) kv_rows_native_kernel(RowArgs a) {
     const uint32_t cpr = a.L.row_bytes >> 4;  // chunks per row
     const uint32_t per_row = a.L.kvh * 2u * cpr;
     const uint32_t row0 = blockIdx.y * NATIVE_GROUP, rows = min(NATIVE_GROUP, a.n - row0);
-    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= rows * per_row) return;
-    uint32_t r = row0 + idx / per_row, w = idx % per_row;
-    uint32_t g = w / (2u * cpr), kv = (w / cpr) & 1u, c = w % cpr;
-    uint32_t block, slot;
-    if (!row_target(a, r, block, slot)) return;
+    const uint32_t total = rows * per_row;
+    const bool pow2 = (cpr & (cpr - 1u)) == 0u && (per_row & (per_row - 1u)) == 0u;
+    const uint32_t cpr_shift = 31u - (uint32_t)__clz((int)cpr), row_shift = 31u - (uint32_t)__clz((int)per_row);
     const uint32_t epc = 16u / a.L.e;  // elements per chunk
-    const float* src = (kv ? a.v_rows : a.k_rows) + (size_t)r * a.row_stride + g * a.L.d + c * epc;
-    uint4 out;
-    if (a.L.dtype == QVX_F32) {
-        out = *reinterpret_cast<const uint4*>(src);
-    } else {
-        float4 lo = *reinterpret_cast<const float4*>(src);
-        float4 hi = *reinterpret_cast<const float4*>(src + 4);
-        uint32_t dt = a.L.dtype;
-        out.x = (uint32_t)narrow16(lo.x, dt) | ((uint32_t)narrow16(lo.y, dt) << 16);
-        out.y = (uint32_t)narrow16(lo.z, dt) | ((uint32_t)narrow16(lo.w, dt) << 16);
-        out.z = (uint32_t)narrow16(hi.x, dt) | ((uint32_t)narrow16(hi.y, dt) << 16);
-        out.w = (uint32_t)narrow16(hi.z, dt) | ((uint32_t)narrow16(hi.w, dt) << 16);
+    const uint32_t dt = a.L.dtype;
+    const uint32_t first = blockIdx.x * (256u * NATIVE_PER_THREAD) + threadIdx.x;
+    float4 lo[NATIVE_PER_THREAD], hi[NATIVE_PER_THREAD];
+    uint32_t at[NATIVE_PER_THREAD], rr[NATIVE_PER_THREAD], ww[NATIVE_PER_THREAD];
+    // The source rows do not depend on where they go: their loads and the targets' loads go out together.
+#pragma unroll
+    for (uint32_t u = 0; u < NATIVE_PER_THREAD; u++) {
+        const uint32_t idx = first + u * 256u;
+        at[u] = 0xffffffffu;
+        if (idx >= total) continue;
+        // (powers of two in every configuration of interest: shifts instead of divisions)
+        const uint32_t r = row0 + (pow2 ? idx >> row_shift : idx / per_row), w = pow2 ? idx & (per_row - 1u) : idx % per_row;
+        rr[u] = r; ww[u] = w;
+        const uint32_t g = pow2 ? w >> (cpr_shift + 1u) : w / (2u * cpr), kv = (pow2 ? w >> cpr_shift : w / cpr) & 1u,
+                       c = pow2 ? w & (cpr - 1u) : w % cpr;
+        const float* src = (kv ? a.v_rows : a.k_rows) + (size_t)r * a.row_stride + g * a.L.d + c * epc;
+        lo[u] = *reinterpret_cast<const float4*>(src);
+        if (dt != QVX_F32) hi[u] = *reinterpret_cast<const float4*>(src + 4);
+        if (a.at_direct) {
+            at[u] = a.at_direct[r];
+        } else {
+            const uint32_t p = a.pos[r];
+            at[u] = a.blocks[a.table_at[r] + p / a.L.B] * a.L.B + p % a.L.B;
+        }
     }
-    uint8_t* dst = a.pool + (uint64_t)block * a.L.block_bytes + (uint64_t)g * 2u * a.L.page_bytes +
-                   (uint64_t)kv * a.L.page_bytes + (uint64_t)slot * a.L.row_bytes + ((c ^ (slot & 7u)) << 4);
-    *reinterpret_cast<uint4*>(dst) = out;
+#pragma unroll
+    for (uint32_t u = 0; u < NATIVE_PER_THREAD; u++) {
+        if (at[u] == 0xffffffffu) continue;
+        const uint32_t block = at[u] / a.L.B, slot = at[u] % a.L.B, w = ww[u];
+        const uint32_t g = pow2 ? w >> (cpr_shift + 1u) : w / (2u * cpr), kv = (pow2 ? w >> cpr_shift : w / cpr) & 1u,
+                       c = pow2 ? w & (cpr - 1u) : w % cpr;
+        uint4 out;
+        if (dt == QVX_F32) {
+            out = make_uint4(__float_as_uint(lo[u].x), __float_as_uint(lo[u].y), __float_as_uint(lo[u].z), __float_as_uint(lo[u].w));
+        } else {
+            out.x = narrow16x2(lo[u].x, lo[u].y, dt);
+            out.y = narrow16x2(lo[u].z, lo[u].w, dt);
+            out.z = narrow16x2(hi[u].x, hi[u].y, dt);
+            out.w = narrow16x2(hi[u].z, hi[u].w, dt);
+        }
+        uint8_t* dst = a.pool + (uint64_t)block * a.L.block_bytes + (uint64_t)g * 2u * a.L.page_bytes +
+                       (uint64_t)kv * a.L.page_bytes + (uint64_t)slot * a.L.row_bytes + ((c ^ (slot & 7u)) << 4);
+        *reinterpret_cast<uint4*>(dst) = out;
+        (void)rr;
+    }
 }
 
 // Any layout, one thread per element.
@@ -102,7 +129,8 @@ int32_t launch_kv_rows(qvx_device* dev, const Layout& L, void* pool, const float
     if (L.layout == QVX_LAYOUT_NATIVE && aligned) {
         const uint32_t per_row = L.kvh * 2u * (L.row_bytes >> 4);
         const uint32_t rows_x = (uint32_t)std::min<size_t>(n, NATIVE_GROUP);
-        dim3 grid((rows_x * per_row + 255u) / 256u, (unsigned)((n + NATIVE_GROUP - 1) / NATIVE_GROUP));
+        const uint32_t span = 256u * NATIVE_PER_THREAD;
+        dim3 grid((rows_x * per_row + span - 1u) / span, (unsigned)((n + NATIVE_GROUP - 1) / NATIVE_GROUP));
         kv_rows_native_kernel<<<grid, 256, 0, s>>>(a);
     } else {
         uint64_t total = (uint64_t)n * 2u * L.kvh * L.d;

@@ -114,6 +114,19 @@ QVX_HD float f16_to_f32(uint16_t h) {
 }
 QVX_HD uint16_t narrow16(float f, uint32_t dtype) { return dtype == QVX_BF16 ? f32_to_bf16(f) : f32_to_f16(f); }
 QVX_HD float widen16(uint16_t h, uint32_t dtype) { return dtype == QVX_BF16 ? bf16_to_f32(h) : f16_to_f32(h); }
+#if defined(__CUDACC__)
+// Two elements at once on the device (x0 in the low half): the hardware's round-to-nearest-even
+// conversion gives the same bits as the integer code above for everything but NaNs, which it
+// canonicalises; those take the integer code.
+__device__ __forceinline__ uint32_t narrow16x2(float x0, float x1, uint32_t dtype) {
+    uint32_t r;
+    if (dtype == QVX_BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(x1), "f"(x0));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(x1), "f"(x0));
+    if (x0 != x0) r = (r & 0xffff0000u) | (uint32_t)narrow16(x0, dtype);
+    if (x1 != x1) r = (r & 0x0000ffffu) | ((uint32_t)narrow16(x1, dtype) << 16);
+    return r;
+}
+#endif
 
 // ---- the device handle ---------------------------------------------------------------------
 struct TimedLaunch {

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 import oracle
-from helpers import Case, XorShift, within
+from helpers import DT, Case, XorShift, within
 from qubivex_b200 import device as qd
 
 pytestmark = pytest.mark.gpu
@@ -511,3 +511,42 @@ def test_independent_host_ops_side_by_side_give_the_same_bits(dev):
     finally:
         for b in bufs:
             b.free()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_narrowing_edge_values_have_the_oracles_bytes(dev, dtype):
+    # The device narrows with the hardware's conversion (NaNs by the spelled-out rule): zeros, f32
+    # subnormals, ties in and around the 16-bit formats' subnormal range, the overflow thresholds,
+    # infinities and NaNs of both signs with payloads must give the oracle's bytes.
+    kvh, d, B = 2, 64, 16
+    bits = [0x00000000, 0x80000000, 0x00000001, 0x807fffff, 0x00800000, 0x3f800000, 0x3f808000, 0x3f818000, 0x3f80ffff,
+            0x3f808001, 0x477fe000, 0x477fefff, 0x477ff000, 0x47800000, 0xc77ff000, 0x7f7fffff, 0xff7fffff, 0x7f800000,
+            0xff800000, 0x7fc00000, 0xffc00001, 0x7f800001, 0xff80ffff, 0x7fffffff, 0x33000000, 0x33000001, 0x33800000,
+            0x33c00000, 0x34000000, 0x387fc000, 0x387fe000, 0x38800000, 0x387fffff, 0x38000000, 0x37ffffff, 0x3effffff,
+            0x7f7f8000, 0x7f7f7fff, 0x00008000, 0x00018000, 0x00017fff, 0x80008001]
+    rng = np.random.default_rng(3)
+    n_rows = 8
+    vals = np.array(bits, dtype=np.uint32)
+    rows = rng.standard_normal((n_rows, 2 * kvh * d), dtype=np.float32)
+    flat = rows.reshape(-1).view(np.uint32)
+    flat[:len(vals)] = vals
+    flat[len(vals):2 * len(vals)] = vals ^ np.uint32(0x80000000)
+    # random bit patterns too (every exponent, many ties are unlikely but signs/NaNs/subnormals are covered)
+    flat[2 * len(vals):2 * len(vals) + 512] = rng.integers(0, 2**32, size=512, dtype=np.uint64).astype(np.uint32)
+    geo_o, geo_d = oracle.geometry(B, kvh, d, DT[dtype], 1), qd.geometry(B, kvh, d, DT[dtype], 1)
+    bb = oracle.block_bytes(geo_o)
+    sync_to = np.array([5, 17, 3, 30, 31, 0, 16, 9], dtype=np.uint32)
+    pool_o = np.zeros(2 * bb, dtype=np.uint8)
+    kv_out = kvh * d
+    rc = oracle.kv_write(pool_o, geo_o, np.zeros((0, kv_out), np.float32), np.zeros((0, kv_out), np.float32), [], [], [], rows, sync_to)
+    assert rc == 0
+    buf = dev.alloc(2 * bb)
+    try:
+        dev.write(buf, 0, np.zeros(2 * bb, dtype=np.uint8))
+        # a sync-only op: no tokens
+        dev.paged_attention(buf, geo_d, 4, np.zeros((0, 4, d), np.float32), np.zeros((0, kv_out), np.float32),
+                            np.zeros((0, kv_out), np.float32), [], [], [], rows, sync_to)
+        got = dev.read(buf, 0, 2 * bb)
+    finally:
+        buf.free()
+    assert np.array_equal(got, pool_o)
