@@ -7,6 +7,7 @@ the C ABI, with the algorithmic bytes each moves: `python -m qubivex_b200.profil
   c5   one GPU's share of the head-sharded shape (8 q / 1 kv head, batch 256, contexts U[1024, 16384])
   c1   the f32 reference-runnable shape (split and exact-order kernels)
   rows the sync / append kernel at prefill and decode sizes
+  static  the fixed-scratch entry point (qvx_attn_decode_static) on the c2 launch
 """
 from __future__ import annotations
 
@@ -88,6 +89,37 @@ def attention_case(dev, name, shape: wl.Shape, lengths, shared_prefix=0, sharers
     del pool
 
 
+def static_case(dev, name, shape: wl.Shape, lengths, seed=1):
+    """The fixed-scratch entry point (qvx_attn_decode_static) on the same kind of launch, timed with stream events."""
+    geo = qd.geometry(shape.block_tokens, shape.kv_heads, shape.head_dim, qd.BF16, qd.LAYOUT_NATIVE)
+    bb = qd.block_bytes(geo)
+    B = shape.block_tokens
+    lengths = np.asarray(lengths, dtype=np.int64)
+    nb = (lengths + B - 1) // B
+    pool_blocks = int(nb.sum()) + 8
+    perm = wl.permutation(pool_blocks, seed)
+    tabs = wl.tables_for(lengths, B, perm)
+    pool = (torch.randn(pool_blocks * bb // 2, device="cuda") * wl.value_scale(shape)).to(torch.bfloat16)
+    s = len(lengths)
+    q = torch.randn((s, shape.heads, shape.head_dim), device="cuda") * wl.value_scale(shape)
+    out = torch.empty_like(q)
+    d_pos, d_blocks, d_at = (torch.from_numpy(a.astype(np.int32)).cuda() for a in (tabs.pos, tabs.blocks, tabs.table_at))
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call():
+        dev.check(dev.lib.qvx_attn_decode_static(dev.h, C.byref(geo), ptr(pool), shape.heads, s, ptr(q), ptr(d_pos), ptr(d_blocks),
+                                                 ptr(d_at), int(tabs.pos.max()), ptr(out), stream))
+    for _ in range(3):
+        call()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    _report(name, wl.algorithmic_bytes(shape, lengths), e0.elapsed_time(e1) / 20 * 1e-3)
+
+
 def rows_case(dev, name, shape: wl.Shape, n_rows, dtype=qd.BF16):
     geo = qd.geometry(shape.block_tokens, shape.kv_heads, shape.head_dim, dtype, qd.LAYOUT_NATIVE)
     bb = qd.block_bytes(geo)
@@ -122,6 +154,8 @@ def main(names):
     rng = np.random.default_rng(7)
     if "c2" in names:
         attention_case(dev, "c2 attention: batch 64, ctx U[1024,4096], 32q/4kv, bf16, B16", wl.C2, rng.integers(1024, 4097, size=64))
+    if "static" in names:
+        static_case(dev, "c2 attention, fixed-scratch entry (20 launches back to back)", wl.C2, np.random.default_rng(7).integers(1024, 4097, size=64))
     if "c3" in names:
         attention_case(dev, "c3 attention: 16 x 32768, 8 share 8192, bf16, B16", wl.C3, [32768] * 16, shared_prefix=8192, sharers=8)
     if "c4" in names:
@@ -146,4 +180,4 @@ def main(names):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1:] or ["c2", "c3", "c4", "c5", "c1", "rows"])
+    main(sys.argv[1:] or ["c2", "static", "c3", "c4", "c5", "c1", "rows"])
