@@ -153,8 +153,9 @@ struct Mail {
     uint32_t seq, head0, nheads, part0, nch, counter, stop, chunk;
 };
 
-// The partial results of a split sequence are merged as a tree of fan-in MERGE_FAN: entry i of
-// level k belongs to node i / MERGE_FAN; the warp that delivers the last entry of a node merges
+// The partial results of a split sequence are merged as a tree of fan-in MERGE_FAN: the n entries
+// of a level are dealt to ceil(n / MERGE_FAN) nodes of as equal a size as possible (9 entries make
+// nodes of 5 and 4, not of 8 and 1); the warp that delivers the last entry of a node merges
 // the node's entries (in entry order) into one entry of level k + 1, or into the output when the
 // level has at most MERGE_FAN entries.  The tree is a function of the chunk count alone, so the
 // sum order is fixed; no merge reads more than MERGE_FAN entries, so the work left after a
@@ -163,6 +164,22 @@ struct Mail {
 #define QVX_MERGE_FAN 8
 #endif
 constexpr uint32_t MERGE_FAN = QVX_MERGE_FAN;
+
+// Where entry `idx` of a level of `n` entries sits: its node, the node's first entry and size.
+struct MergeNode {
+    uint32_t node, first, size;
+};
+__host__ __device__ inline MergeNode merge_node_of(uint32_t idx, uint32_t n) {
+    const uint32_t nodes = (n + MERGE_FAN - 1) / MERGE_FAN, base = n / nodes, extra = n % nodes;
+    const uint32_t split = extra * (base + 1);  // the first `extra` nodes hold one entry more
+    MergeNode m;
+    if (idx < split) {
+        m.node = idx / (base + 1); m.first = m.node * (base + 1); m.size = base + 1;
+    } else {
+        m.node = extra + (idx - split) / base; m.first = split + (m.node - extra) * base; m.size = base;
+    }
+    return m;
+}
 
 // Entries and counters one (sequence, group) of `nch` chunks needs, over all levels.
 __host__ __device__ inline uint32_t merge_entries_total(uint32_t nch) {
@@ -268,7 +285,8 @@ __device__ __forceinline__ bool wait_published(const uint32_t* published, uint32
 template <int D>
 __device__ __forceinline__ bool fold_ahead(const StreamArgs& a, const Mail& it, uint32_t lane, Running<D>& r) {
     constexpr uint32_t PART_STRIDE = 8 * D + 16;
-    const uint32_t node = it.chunk / MERGE_FAN, first = node * MERGE_FAN, size = min(MERGE_FAN, it.nch - first), mine = it.chunk - first;
+    const MergeNode mn = merge_node_of(it.chunk, it.nch);
+    const uint32_t node = mn.node, first = mn.first, size = mn.size, mine = it.chunk - first;
     if (size < 2) return false;
     const uint32_t* claimed = a.counters + it.counter + 2 * node;
     // Both words in one round trip: lane 0 reads `claimed`, lane 1 `published`.
@@ -315,7 +333,8 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
     }
     uint32_t n = it.nch, idx = it.chunk, part_base = it.part0, cnt_base = it.counter;
     for (;;) {
-        const uint32_t node = idx / MERGE_FAN, first = node * MERGE_FAN, size = min(MERGE_FAN, n - first), mine = idx - first;
+        const MergeNode mn = merge_node_of(idx, n);
+        const uint32_t node = mn.node, first = mn.first, size = mn.size, mine = idx - first;
         uint32_t* claimed = a.counters + cnt_base + 2 * node;
         uint32_t* published = claimed + 1;
         float* p0 = a.partials + (size_t)(part_base + first) * PART_STRIDE;
