@@ -153,9 +153,10 @@ struct Mail {
     uint32_t seq, head0, nheads, part0, nch, counter, stop, chunk;
 };
 
-// The partial results of a split sequence are merged as a tree of fan-in MERGE_FAN: the n entries
-// of a level are dealt to ceil(n / MERGE_FAN) nodes of as equal a size as possible (9 entries make
-// nodes of 5 and 4, not of 8 and 1); the warp that delivers the last entry of a node merges
+// The partial results of a split sequence are merged as a tree of fan-in MERGE_FAN: entry i of
+// level k belongs to node i / MERGE_FAN (full nodes first, the remainder last: a sequence's last
+// chunk, which usually arrives last, then finds little left to merge -- dealing the entries to nodes
+// of equal size, QVX_MERGE_BALANCED, measured 1 % slower); the warp that delivers the last entry of a node merges
 // the node's entries (in entry order) into one entry of level k + 1, or into the output when the
 // level has at most MERGE_FAN entries.  The tree is a function of the chunk count alone, so the
 // sum order is fixed; no merge reads more than MERGE_FAN entries, so the work left after a
@@ -170,6 +171,12 @@ struct MergeNode {
     uint32_t node, first, size;
 };
 __host__ __device__ inline MergeNode merge_node_of(uint32_t idx, uint32_t n) {
+#ifndef QVX_MERGE_BALANCED
+    MergeNode p;
+    p.node = idx / MERGE_FAN; p.first = p.node * MERGE_FAN; p.size = n - p.first < MERGE_FAN ? n - p.first : MERGE_FAN;
+    return p;
+#endif
+    // (experiments) nodes of as equal a size as possible: 9 entries make nodes of 5 and 4, not of 8 and 1
     const uint32_t nodes = (n + MERGE_FAN - 1) / MERGE_FAN, base = n / nodes, extra = n % nodes;
     const uint32_t split = extra * (base + 1);  // the first `extra` nodes hold one entry more
     MergeNode m;
