@@ -12,12 +12,22 @@ partitions by sequence: no collective in it), `value` is all ranks' tokens over 
 rank's time, scaling "weak".
 
 One JSON line on stdout:
-  value      tokens/s with every input already in device memory (one launch per layer: append fused into attention)
-  e2e        tokens/s through the host-memory call of the C ABI (pinned host buffers in, outputs
-             back to the host), copies inside the timed region
-  roofline   the attention kernel's algorithmic bytes per launch over its mean duration (CUDA
-             events around every launch, inside the timed region), against the measured copy
-             bandwidth of MEASURED_PEAKS.json
+  value      tokens/s with every input already in device memory (one launch per layer: append fused
+             into attention).  The K steps are timed as one block; the block is repeated until the
+             timed region lasts at least a second, so the clock record holds tens of samples.  The
+             block tables and work lists of every step are built and uploaded (qvx_tables_create)
+             before the clock starts: `value` does not pay for them, `e2e` does.
+  e2e        tokens/s through the host-memory call of the C ABI the reference's runtime would make:
+             one synchronous qvx_paged_attention_host per layer (DiscreteDevice::routed_moe is complete
+             on return, and layer l + 1's query does not exist before layer l has returned), pinned
+             host buffers in, outputs back to the host, copies inside the timed region.
+             `e2e.pipelined` is the same step through qvx_paged_attention_host_async x layers and one
+             qvx_wait: what a caller that has all the layers' inputs at hand could reach.
+  roofline   the attention kernel's algorithmic bytes per launch over its mean duration in the timed
+             region (nothing else runs there), against the measured copy bandwidth of
+             MEASURED_PEAKS.json
+  parity_sample  one (sequence, layer) of the last timed step, read back with its blocks of the
+             pool and checked against the CPU oracle after the clock has stopped
   cpu_baseline  the CPU restatement of the reference's own path, timed on this host (rank 0, N = 1)
 
 --impl reference times only that CPU path, on all host threads, as the reference arm.
@@ -51,6 +61,14 @@ DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.012
 
 def env_int(name: str, default: int) -> int:
     return int(os.environ.get(name, default))
+
+
+def config_of(shape: "wl.Shape", layers: int) -> dict:
+    """The workload's description: the same keys and values in both arms."""
+    return {"workload": shape.name, "layers": layers, "batch_per_gpu": shape.batch, "heads": shape.heads,
+            "kv_heads": shape.kv_heads, "head_dim": shape.head_dim, "block_tokens": shape.block_tokens,
+            "context": [shape.ctx_lo, shape.ctx_hi], "partition": "by sequence, no collective",
+            "l2": "each launch reads more than 300 MiB of KV, once (the L2 holds 126 MB): no flush between iterations"}
 
 
 def measured_peak_gbs() -> tuple[float, str]:
@@ -134,8 +152,11 @@ class CpuSample:
             dt = time.perf_counter() - t0
             if dt >= target_s or reps >= 4096:
                 break
-        text = (f"{self.n} sequences (contexts {int(lens.min())}-{int(lens.max())}) x 1 layer x 1 decode step, repeated {reps}x "
-                f"({dt:.1f} s); tokens/s = 1 / ({self.shape.layers} layers x seconds per sequence-layer)")
+        text = (f"{self.n} of the {self.shape.batch} sequences (contexts {int(lens.min())}-{int(lens.max())}) x 1 of the "
+                f"{self.shape.layers} layers x 1 decode step, repeated {reps}x ({dt:.1f} s) on {self.threads} threads, one task per "
+                f"(token, KV head): its rows gathered from the paged pool once, then attend per query head; "
+                f"extrapolated: tokens/s = 1 / ({self.shape.layers} layers x seconds per sequence-layer), "
+                f"i.e. the sample is 1/{self.shape.batch // self.n} of the batch x 1/{self.shape.layers} of the layers of a step")
         return dt / (reps * self.n), text
 
 
@@ -160,9 +181,7 @@ def run_reference(args, rank: int, world: int) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": shape.batch / value * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": shape.name, "layers": shape.layers, "batch": shape.batch, "heads": shape.heads,
-                   "kv_heads": shape.kv_heads, "head_dim": shape.head_dim, "block_tokens": shape.block_tokens,
-                   "context": [shape.ctx_lo, shape.ctx_hi]},
+        "config": config_of(shape, shape.layers),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": text},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -171,6 +190,28 @@ def run_reference(args, rank: int, world: int) -> None:
 
 
 # ---------------------------------------------------------------------------------------------
+def parity_sample(dev, pool, geo, shape, lengths, blocks, table_at, q_dev, out_dev, seq: int) -> dict:
+    """Sequence `seq` of the last launch of the timed region against the CPU oracle: its blocks of the
+    pool are read back (they hold the row the launch appended), the oracle attends over them with the
+    launch's query, and the launch's output for the sequence must be within the 16-bit tolerance."""
+    import oracle
+
+    B = shape.block_tokens
+    n = int(lengths[seq]) + 1                      # positions 0..=pos
+    ids = blocks[int(table_at[seq]):int(table_at[seq]) + (n + B - 1) // B]
+    geo_o = oracle.geometry(B, shape.kv_heads, shape.head_dim, oracle.BF16, oracle.LAYOUT_NATIVE)
+    bb = oracle.block_bytes(geo_o)
+    host_pool = np.concatenate([dev.read(pool, int(b) * bb, bb) for b in ids])
+    q1 = q_dev[seq:seq + 1].cpu().numpy()
+    rc, want = oracle.attn_decode(host_pool, geo_o, shape.heads, q1, np.array([n - 1], dtype=np.uint32),
+                                  np.arange(len(ids), dtype=np.uint32), np.zeros(1, dtype=np.uint32), threads=os.cpu_count() or 1)
+    got = out_dev[seq].cpu().numpy()
+    err = np.abs(got.astype(np.float64) - want[0].astype(np.float64))
+    ok = rc == 0 and bool(np.all(err <= 2e-3 + 1e-2 * np.abs(want[0])))
+    return {"sequence": int(seq), "layer": "last", "positions": n, "max_abs_err": float(err.max()),
+            "tolerance": "2e-3 + 1e-2 * |oracle|", "ok": ok}
+
+
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     import torch
 
@@ -265,31 +306,45 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     for t in range(W):
         step(t)
     barrier()
+    # One untimed block of the K steps tells how many repeats of the block make a second.
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for t in range(W, W + K):
+        step(t)
+    p1.record()
+    barrier()
+    repeats = torch.tensor([max(1, int(np.ceil(args.min_seconds * 1e3 / max(p0.elapsed_time(p1), 1e-3))))], device="cuda")
+    if dist is not None:
+        dist.all_reduce(repeats, op=dist.ReduceOp.MAX)
+    R = int(repeats.item())
     dev.reset_kernel_times()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_load0 = time.perf_counter()
     e0.record()
-    for t in range(W, W + K):
-        step(t)
+    for _ in range(R):  # the K steps again: the same rows land on the same positions, the pool does not change
+        for t in range(W, W + K):
+            step(t)
     e1.record()
     barrier()
     clocks = sampler.stop(t_load0, time.perf_counter())
     ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
     if dist is not None:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_total = float(ms.item())
+    ms_total = float(ms.item()) / R      # per block of K steps
     kt = dev.kernel_times()
     value = world * s * K / (ms_total / 1e3)
     attn_launches, attn_ns = kt["attn"]
+    parity = parity_sample(dev, pool, geo, shape, lengths + (W + K - 1), layer_blocks[layers - 1], table_at, q[W + K - 1], out,
+                           SEED % s)
     algo = float(np.mean([wl.algorithmic_bytes(shape, lengths + t + 1) for t in range(W, W + K)]))
     # The timed region holds nothing but this kernel's launches, back to back on one stream: its
     # CUDA-event duration over their number is the launch duration the throughput is made of.  The
     # events the library puts around every 64th launch give the duration of a launch taken alone
     # (no overlap with its neighbours' ends, plus the events themselves): reported beside it.
-    launch_us = ms_total * 1e3 / (K * layers)
+    launch_us = ms_total * 1e3 / (K * layers)  # (ms_total is per block of K steps)
     achieved = algo / (launch_us * 1e-6) / 1e9
     peak, peak_kind = measured_peak_gbs()
-    launches = K * layers  # one launch per layer-step: the append rides in the attention kernel
+    launches = R * K * layers  # one launch per layer-step: the append rides in the attention kernel
     for row in tabs:
         for tb in row:
             lib.qvx_tables_free(tb)
@@ -304,37 +359,42 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     # raw addresses once: the buffers live for the whole run
     p_q, p_k, p_v, p_ta, p_geo = ptr(qh), ptr(kh), ptr(vh), ptr(table_at), C.byref(geo)
     p_blocks, p_out = [ptr(b) for b in layer_blocks], [ptr(o) for o in oh]
-    host_call = lib.qvx_paged_attention_host_async
-    # consecutive ops serve different layers (disjoint blocks): they may overlap each other's ends
+    # consecutive ops serve different layers (disjoint blocks): queued together they may overlap each other's ends
     host_variant = qd.ATTN_AUTO | (qd.ATTN_POOL_SETTLED if layers >= 2 else 0)
 
-    def step_host(t: int):
+    def step_host(t: int, pipelined: bool):
         nonlocal h2d, d2h
         pos = (lengths + t).astype(np.uint32)
         p_pos = ptr(pos)
+        call = lib.qvx_paged_attention_host_async if pipelined else lib.qvx_paged_attention_host
         for l in range(layers):
-            rc = host_call(dev.h, pool.handle, p_geo, heads, s, p_q, p_k, p_v, p_pos, p_blocks[l], blocks_per_layer, p_ta, None, None, 0,
-                           p_out[l], host_variant)
+            rc = call(dev.h, pool.handle, p_geo, heads, s, p_q, p_k, p_v, p_pos, p_blocks[l], blocks_per_layer, p_ta, None, None, 0,
+                      p_out[l], host_variant if pipelined else qd.ATTN_AUTO)
             if rc:
                 dev.check(rc)
-        dev.wait()
+        if pipelined:
+            dev.wait()
         h2d = layers * (qh.numel() * 4 + kh.numel() * 8 + pos.nbytes + table_at.nbytes + layer_blocks[0].nbytes)
         d2h = layers * oh[0].numel() * 4
 
-    for t in range(W + K, W + K + We):
-        step_host(t)
-    barrier()
-    each_ms = []
-    t0 = time.perf_counter()
-    for t in range(W + K + We, W + K + We + Ke):
-        step_host(t)
-        each_ms.append(time.perf_counter())
-    torch.cuda.synchronize()
-    el = torch.tensor([time.perf_counter() - t0], device="cuda")
-    each_ms = [round(1e3 * (b - a), 3) for a, b in zip([t0] + each_ms[:-1], each_ms)]
-    if dist is not None:
-        dist.all_reduce(el, op=dist.ReduceOp.MAX)
-    e2e_value = world * s * Ke / float(el.item())
+    def time_host(first: int, pipelined: bool):
+        for t in range(first, first + We):
+            step_host(t, pipelined)
+        barrier()
+        each, t0 = [], time.perf_counter()
+        for t in range(first + We, first + We + Ke):
+            step_host(t, pipelined)
+            each.append(time.perf_counter())
+        torch.cuda.synchronize()
+        el = torch.tensor([time.perf_counter() - t0], device="cuda")
+        if dist is not None:
+            dist.all_reduce(el, op=dist.ReduceOp.MAX)
+        each = [round(1e3 * (b - a), 3) for a, b in zip([t0] + each[:-1], each)]
+        return world * s * Ke / float(el.item()), each
+
+    # Both variants step over the same positions (the second rewrites the rows the first wrote).
+    e2e_pipelined, each_pipelined = time_host(W + K, True)
+    e2e_value, each_ms = time_host(W + K, False)
     checksum = float(sum(float(o[0, 0, 0]) for o in oh))
     assert np.isfinite(checksum)
 
@@ -342,18 +402,23 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": ms_total / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": shape.name, "layers": layers, "batch_per_gpu": s, "heads": heads, "kv_heads": kvh, "head_dim": d,
-                   "block_tokens": B, "context": [shape.ctx_lo, shape.ctx_hi], "partition": "by sequence, no collective",
-                   "l2": f"each launch reads {algo / 2**20:.0f} MiB of KV, more than the 126 MB L2; no flush needed",
-                   "pool_gib": pool_blocks * bb / 2**30},
+        "config": config_of(shape, layers),
+        "timed_region": {"blocks_of_k_steps": R, "seconds": ms_total * R / 1e3, "pool_gib": pool_blocks * bb / 2**30,
+                         "kv_mib_per_launch": algo / 2**20,
+                         "value_excludes": "qvx_tables_create (work lists built and uploaded for every step before the clock "
+                                           "starts); e2e pays for it in every op"},
         "roofline": {"bound": "hbm", "kernel": "attn_stream_kernel (paged decode attention)", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "frac_of_8000": achieved / 8000.0,
                      "traffic": algo * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE, "algorithmic_bytes_per_launch": algo,
-                     "launch_us": launch_us, "launches": int(K * layers),
+                     "launch_us": launch_us, "launches": int(launches),
                      "launch_alone_us": attn_ns / max(attn_launches, 1) / 1e3, "launches_timed_alone": int(attn_launches),
                      "kernels_us_per_launch": {k: (v[1] / v[0] / 1e3 if v[0] else 0.0) for k, v in kt.items() if v[0]}},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "call": "qvx_paged_attention_host_async x layers + qvx_wait per step", "ms_each_step": each_ms},
+                "call": "qvx_paged_attention_host x layers per step: synchronous, one op per layer, as DiscreteDevice::routed_moe",
+                "ms_each_step": each_ms,
+                "pipelined": {"value": e2e_pipelined, "call": "qvx_paged_attention_host_async x layers + qvx_wait per step",
+                              "ms_each_step": each_pipelined}},
+        "parity_sample": parity,
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
@@ -379,6 +444,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 48 (debugging only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="the K steps are repeated until the timed region lasts this long")
     args = ap.parse_args()
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     if args.impl == "reference":

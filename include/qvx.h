@@ -15,6 +15,12 @@
  *  - `stream` is a `cudaStream_t` passed as `void*`; NULL is the legacy default stream.
  *    Calls whose name ends in `_host` are synchronous: complete on return, as
  *    `DiscreteDevice::routed_moe` is (crates/qubivex-compute/src/discrete.rs:561-569).
+ *  - What a kernel finds out too late for a return code (a block id in device memory that is not
+ *    the pool's, a position beyond a bound the caller gave, a bounded wait that ran out) goes
+ *    into a per-device status word.  The host reads it at its next wait on that device
+ *    (`qvx_wait`, any synchronous `_host` call, `qvx_get_kernel_times`), returns
+ *    QVX_ERR_DEVICE with the reason in `qvx_last_error`, and clears it: the word is sticky
+ *    until then, and the report may land on a later, unrelated call.
  *  - There is no CPU fallback anywhere: without a CUDA device `qvx_open` fails.
  *  - Paths cited are relative to the reference project's root.
  */
@@ -135,13 +141,18 @@ int32_t qvx_reset_kernel_times(qvx_device *dev);
  * (crates/qubivex-backend-vulkan/shaders/kv_sync.comp:1-51) and the sync loop of `put`
  * (crates/qubivex-backend-cpu/src/sim.rs:391-393).  rows: n x 2*kv_out f32 (key row, value
  * row); sync_to[r] = block * block_tokens + slot.  Positions must be distinct (the _host
- * call below resolves duplicates the reference's way: the later row wins). */
+ * call below resolves duplicates the reference's way: the later row wins).  `pool_blocks` is
+ * the number of blocks `pool` holds: sync_to lives in device memory, so the kernel does the
+ * check sim.rs:372-376 does on the host — a row for a block at or past pool_blocks is not
+ * written and the device status reports it. */
 int32_t qvx_kv_sync(qvx_device *dev, const qvx_geometry *geo, void *pool, size_t pool_blocks,
                     const float *rows, const uint32_t *sync_to, size_t n, void *stream);
 
 /* Each token's new key and value row at its position: the store of `attn_prelude.comp`
  * (shaders/attn_prelude.comp:92-104, :169-173) and sim.rs:394-398.  k_new, v_new:
- * s x kv_out f32.  Token t's row goes to blocks[table_at[t] + pos[t] / B], slot pos[t] % B. */
+ * s x kv_out f32.  Token t's row goes to blocks[table_at[t] + pos[t] / B], slot pos[t] % B.
+ * A row whose block id is at or past pool_blocks is not written (device status, as above);
+ * the tables' own extent is the caller's to get right. */
 int32_t qvx_kv_append(qvx_device *dev, const qvx_geometry *geo, void *pool, size_t pool_blocks,
                       const float *k_new, const float *v_new, const uint32_t *pos,
                       const uint32_t *blocks, const uint32_t *table_at, size_t s, void *stream);
@@ -234,7 +245,8 @@ int32_t qvx_attn_prelude(qvx_device *dev, const qvx_geometry *geo, size_t heads,
 /* Whole-block copies src[i] -> dst[i]: the copy of a shared block before the first
  * divergent append, and the moves of a compaction pass.  No counterpart in the reference,
  * which copies a whole cache (crates/qubivex-arch/src/lib.rs:409-432) and never moves a
- * block.  src and dst are device arrays; no dst may also be a src or another dst. */
+ * block.  src and dst are device arrays; no dst may also be a src or another dst.  A move
+ * with either id at or past pool_blocks is skipped whole (device status, as above). */
 int32_t qvx_block_copy(qvx_device *dev, const qvx_geometry *geo, void *pool, size_t pool_blocks,
                        const uint32_t *src, const uint32_t *dst, size_t n, void *stream);
 

@@ -423,10 +423,13 @@ int qvo_paged_attention(uint8_t *pool, size_t pool_blocks, const qvo_geometry *g
     return QVO_OK;
 }
 
-/* The host path's shape of the same arithmetic: one task per (token, head) calling
- * `attend` on that head's keys and values (crates/qubivex-arch/src/lib.rs:1304-1320,
- * rayon's par_chunks_mut), here read straight from the paged pool.  Same bits as
- * qvo_attn_decode; `threads` workers take (token, head) tasks from a shared counter. */
+/* The host path's shape of the same arithmetic: `attend` once per (token, head) on that head's
+ * keys and values (crates/qubivex-arch/src/lib.rs:1304-1320, rayon's par_chunks_mut over
+ * (token, head)).  The reference's host cache holds each KV head's rows contiguously, so its
+ * tasks read them in place; here they live in the paged pool, so a task is one (token, KV head):
+ * it gathers that head's rows once and runs `attend` for every query head of the group on them
+ * (the gather is not paid once per query head).  Same bits as qvo_attn_decode; `threads` workers
+ * take tasks from a shared counter. */
 typedef struct {
     const uint8_t *pool; const qvo_geometry *geo; size_t heads, s;
     const float *q; const uint32_t *pos, *blocks, *table_at; float *att;
@@ -435,14 +438,14 @@ typedef struct {
 
 static void *par_worker(void *arg) {
     par_job *j = arg;
-    size_t d = j->geo->head_dim, group = j->heads / j->geo->kv_heads, q_out = j->heads * d;
+    size_t d = j->geo->head_dim, kvh = j->geo->kv_heads, group = j->heads / kvh, q_out = j->heads * d;
     float *k = NULL, *v = NULL, *scores = NULL; size_t cap = 0;
     for (;;) {
         pthread_mutex_lock(&j->mu);
         size_t task = j->next++;
         pthread_mutex_unlock(&j->mu);
-        if (task >= j->s * j->heads) break;
-        size_t t = task / j->heads, hd = task % j->heads, g = hd / group;
+        if (task >= j->s * kvh) break;
+        size_t t = task / kvh, g = task % kvh;
         size_t n = (size_t)j->pos[t] + 1;
         if (n > cap) {
             free(k); free(v); free(scores);
@@ -453,7 +456,8 @@ static void *par_worker(void *arg) {
             load_row(j->pool, j->geo, to, 0, g, k + p * d);
             load_row(j->pool, j->geo, to, 1, g, v + p * d);
         }
-        qvo_attend(j->q + t * q_out + hd * d, k, v, d, n - 1, j->att + t * q_out + hd * d, scores);
+        for (size_t hd = g * group; hd < (g + 1) * group; hd++)
+            qvo_attend(j->q + t * q_out + hd * d, k, v, d, n - 1, j->att + t * q_out + hd * d, scores);
     }
     free(k); free(v); free(scores);
     return NULL;

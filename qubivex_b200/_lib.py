@@ -155,20 +155,19 @@ def declared_symbols() -> list[str]:
     return sorted(set(re.findall(r"\b(qvx_[a-z0-9_]+)\s*\(", text)) - {"qvx_release_fn"})
 
 
-_lib = None
+_libs: dict[bool, C.CDLL] = {}
 
 
-def load() -> C.CDLL:
-    """The library, built first if absent.  Raises when it cannot be loaded."""
-    global _lib
-    if _lib is None:
-        path = _build.LIB
+def load(experiments: bool = False) -> C.CDLL:
+    """The library (or its experiment build), built first if absent.  Raises when it cannot be loaded."""
+    if experiments not in _libs:
+        path = _build.LIB_EXPERIMENTS if experiments else _build.LIB
         if not path.exists():
-            _build.build()
+            _build.build(experiments=experiments)
         lib = C.CDLL(str(path))
         for name, (res, args) in PROTOTYPES.items():
             fn = getattr(lib, name)  # AttributeError here = the build is stale or broken
             fn.restype = res
             fn.argtypes = args
-        _lib = lib
-    return _lib
+        _libs[experiments] = lib
+    return _libs[experiments]

@@ -17,12 +17,17 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 ROOT = PKG.parent
 CSRC = PKG / "csrc"
-# QVX_LIB / QVX_NVCC_EXTRA build and load a variant library (kernel experiments); unset, the
-# shipped library is qubivex_b200/lib/libqvx_cuda.so.
-LIB = Path(os.environ["QVX_LIB"]).resolve() if os.environ.get("QVX_LIB") else PKG / "lib" / "libqvx_cuda.so"
-OBJ = ROOT / "build" / ("obj-" + LIB.stem if os.environ.get("QVX_LIB") else "obj")
+# The shipped library, and the experiment build of the same sources (-DQVX_EXPERIMENTS: the chunk and
+# run-length rules and the bf16 remainder pass can be changed through the environment; the tests that
+# show which of those move no bit, and the profiling drivers, load it).
+LIB = PKG / "lib" / "libqvx_cuda.so"
+LIB_EXPERIMENTS = PKG / "lib" / "libqvx_cuda_experiments.so"
+# QVX_LIB / QVX_NVCC_EXTRA build one more variant (kernel experiments) and make it the library loaded.
+if os.environ.get("QVX_LIB"):
+    LIB = Path(os.environ["QVX_LIB"]).resolve()
 EXTRA = os.environ.get("QVX_NVCC_EXTRA", "").split()
 
+LINK: list[str] = []
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 SOURCES = {
@@ -52,16 +57,20 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    OBJ.mkdir(parents=True, exist_ok=True)
-    LIB.parent.mkdir(parents=True, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, experiments: bool = False) -> Path:
+    """Compiles what is stale and links the library; `experiments` builds libqvx_cuda_experiments.so."""
+    lib = LIB_EXPERIMENTS if experiments else LIB
+    extra_flags = ["-DQVX_EXPERIMENTS"] if experiments else EXTRA
+    obj_dir = ROOT / "build" / ("obj-" + lib.stem)
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    lib.parent.mkdir(parents=True, exist_ok=True)
     headers = list(CSRC.glob("*.cuh")) + [ROOT / "include" / "qvx.h", Path(__file__)]
     jobs = []
     for name, extra in SOURCES.items():
         src = CSRC / name
-        obj = OBJ / (name.rsplit(".", 1)[0] + ".o")
+        obj = obj_dir / (name.rsplit(".", 1)[0] + ".o")
         if force or _stale(obj, [src] + headers):
-            cmd = [nvcc(), *ARCH, *COMMON, *extra, *EXTRA]
+            cmd = [nvcc(), *ARCH, *COMMON, *extra, *extra_flags]
             if verbose:
                 cmd += ["-Xptxas", "-v"]
             cmd += ["-c", str(src), "-o", str(obj)]
@@ -78,16 +87,16 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 sys.stderr.write(f"--- {name}\n{r.stdout}{r.stderr}")
             if r.returncode:
                 raise RuntimeError(f"nvcc failed on {name}")
-    objs = [OBJ / (n.rsplit(".", 1)[0] + ".o") for n in SOURCES]
-    if force or jobs or _stale(LIB, objs):
-        cmd = [nvcc(), *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]
+    objs = [obj_dir / (n.rsplit(".", 1)[0] + ".o") for n in SOURCES]
+    if force or jobs or _stale(lib, objs):
+        cmd = [nvcc(), *ARCH, "-shared", "-o", str(lib), *map(str, objs), "-cudart", "static", *LINK]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    out = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
-    print(out)
+    for x in (False, True):
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, experiments=x))

@@ -11,8 +11,6 @@ namespace qvx {
 constexpr int TILE = 16;              // positions per tile
 constexpr uint32_t NO_PART = 0xffffffffu;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
-// Status word values a kernel can leave (0 = fine).
-constexpr int STATUS_WAIT_TIMEOUT = 1;
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -47,6 +45,17 @@ __device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void* src, uin
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
         "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar), "l"(policy)
         : "memory");
+}
+// Asks the L2 to fetch `bytes` (a multiple of 16) at `src` (16-byte aligned); nothing waits for it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(src)), "r"(bytes) : "memory");
+}
+// 16 bytes global -> shared through the L2, asynchronously: no register holds the data meanwhile.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(__cvta_generic_to_global(src)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 __device__ __forceinline__ void st_global_hint(float4* addr, float4 v, uint64_t policy) {
     asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(__cvta_generic_to_global(addr)), "f"(v.x),

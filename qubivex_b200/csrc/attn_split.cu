@@ -365,11 +365,19 @@ uint32_t attn_counters_per_group(const Layout& L, uint32_t nch) { return L.dtype
 template <typename K>
 static int32_t launch_one(qvx_device* dev, K kernel, const SplitArgs& a, unsigned grid, uint32_t smem,
                           cudaStream_t s) {
-    static thread_local K configured = nullptr;  // one opt-in per kernel instantiation and thread
-    if (configured != kernel) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return check_cuda(dev, e, "split attention shared memory");
-        configured = kernel;
+    // The opt-in belongs to the device's context: once per device for each kernel instantiation
+    // (this function is instantiated per kernel type; the caller holds dev->mu, the table has its own lock
+    // because two devices' callers may come here together).
+    static std::mutex mu;
+    static K configured[64] = {};
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        K& done = configured[dev->ordinal & 63];
+        if (done != kernel) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return check_cuda(dev, e, "split attention shared memory");
+            done = kernel;
+        }
     }
     kernel<<<grid, THREADS, smem, s>>>(a);
     return check_cuda(dev, cudaGetLastError(), "split attention launch");

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(STHREADS, 3) attn_static_kernel(StaticArgs a) 
     const uint32_t nch = (len + STATIC_CHUNK_TOKENS - 1) / STATIC_CHUNK_TOKENS;
     if (chunk >= nch) return;
     if (nch > a.max_chunks) {  // the caller's bound on the positions was too small: refuse, write nothing
-        if (threadIdx.x == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT + 1);
+        if (threadIdx.x == 0) atomicExch(a.status, STATUS_POSITION_BOUND);
         return;
     }
     const uint32_t tokens = min(STATIC_CHUNK_TOKENS, len - chunk * STATIC_CHUNK_TOKENS);
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(STHREADS, 3) attn_static_kernel(StaticArgs a) 
     __threadfence();
     // The last chunk of this (sequence, group) to arrive: merge all of them, in chunk order.
     const float* p0 = a.partials + (size_t)pair * a.max_chunks * PS;
-    float* msm = reinterpret_cast<float*>(smem);  // [nch][8] maxima then weights; nch <= max_chunks <= 2048
+    float* msm = reinterpret_cast<float*>(smem);  // [nch][8] maxima then weights, [nch][8] sums, [8]: nch <= max_chunks <= 1000 fits the rings
     float* lsm = msm + nch * 8;
     float* Lsm = lsm + nch * 8;
     for (uint32_t i = threadIdx.x; i < nch * 16; i += STHREADS) {
@@ -279,14 +279,19 @@ extern int* device_status_word(qvx_device* dev);
 static std::mutex g_static_mu;
 static void* g_static_ptr[64];
 
+// `ordinal`: the device that is current.  The shared-memory opt-in belongs to the device's context, so it
+// is made once per device and per kernel instantiation (under g_static_mu's caller-side lock: dev->mu).
 template <int DT, int D, bool PRECISE>
-static cudaError_t launch_static(const StaticArgs& a, dim3 grid, cudaStream_t s) {
+static cudaError_t launch_static(int ordinal, const StaticArgs& a, dim3 grid, cudaStream_t s) {
     auto kernel = attn_static_kernel<DT, D, PRECISE>;
-    static thread_local bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StaticSmem<D>::total);
-        if (e != cudaSuccess) return e;
-        configured = true;
+    static bool configured[64] = {};
+    {
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!configured[ordinal & 63]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StaticSmem<D>::total);
+            if (e != cudaSuccess) return e;
+            configured[ordinal & 63] = true;
+        }
     }
     kernel<<<grid, STHREADS, StaticSmem<D>::total, s>>>(a);
     return cudaGetLastError();
@@ -357,9 +362,9 @@ extern "C" int32_t qvx_attn_decode_static(qvx_device* dev, const qvx_geometry* g
     a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;
     dim3 grid((unsigned)max_chunks, ngroups, (unsigned)s);
     e = cudaErrorInvalidValue;
-    if (L.dtype == QVX_BF16 && L.d == 128) e = launch_static<QVX_BF16, 128, true>(a, grid, st);
-    if (L.dtype == QVX_BF16 && L.d == 64) e = launch_static<QVX_BF16, 64, true>(a, grid, st);
-    if (L.dtype == QVX_F16 && L.d == 128) e = launch_static<QVX_F16, 128, false>(a, grid, st);
-    if (L.dtype == QVX_F16 && L.d == 64) e = launch_static<QVX_F16, 64, false>(a, grid, st);
+    if (L.dtype == QVX_BF16 && L.d == 128) e = launch_static<QVX_BF16, 128, true>(dev->ordinal, a, grid, st);
+    if (L.dtype == QVX_BF16 && L.d == 64) e = launch_static<QVX_BF16, 64, true>(dev->ordinal, a, grid, st);
+    if (L.dtype == QVX_F16 && L.d == 128) e = launch_static<QVX_F16, 128, false>(dev->ordinal, a, grid, st);
+    if (L.dtype == QVX_F16 && L.d == 64) e = launch_static<QVX_F16, 64, false>(dev->ordinal, a, grid, st);
     return check_cuda(dev, e, "qvx_attn_decode_static launch");
 }

@@ -25,14 +25,17 @@
 //     m16n8k16 with K as the A operand straight from the swizzled page), then
 //     O^T += V^T P^T (V through ldmatrix.trans, P transposed in registers by movmatrix).
 //     Every key and value byte is read from shared memory exactly once.
-//   - At the end of an item the consumers merge their states through shared memory (two
-//     named barriers among themselves; the producer keeps streaming the next item meanwhile)
-//     and write the output, or the chunk's partial result.
-//   - An epilogue warp per CTA takes over from there for a sequence that was split into
-//     several chunks: the device-wide fence, the count of the chunk's arrival (one counter per
-//     (sequence, group); nobody waits on it) and, in whichever CTA the last chunk arrives, the
-//     merge of the partials in chunk order, so the sum order is fixed.  The consumers are on
-//     the next item's tiles meanwhile.
+//   - The consumer warps never wait for one another.  At the end of a chunk each leaves its state
+//     (maxima, row sums, unnormalised outputs over the tiles it took) in one of two buffers in
+//     shared memory, arrives on the buffer's mbarrier and goes on with the next chunk's tiles.
+//   - An epilogue warp per CTA puts a chunk together: it merges the consumers' states in the order
+//     of the tiles' places in the chunk and writes the output (a sequence in one chunk) or climbs
+//     the merge tree of the sequence's chunks: an arrival takes a number from its node's
+//     `claimed` word; every arrival but the node's last stores its entry and adds to `published`
+//     (nothing waits for that); the last folds the node's entries in entry order -- the ones
+//     before its own already while its chunk is still streaming, when they are all there -- and
+//     writes the output or the next level's entry.  The only wait on another CTA is the bounded
+//     one of a node's last arrival for entries already claimed.
 //
 // bf16 carries 8 mantissa bits: queries and probabilities go through the tensor cores as a
 // 16-bit value plus a 16-bit remainder (two passes), which keeps the result within 1e-5 of the
@@ -62,7 +65,20 @@ constexpr int REC_SLOTS = 4;
 #define QVX_FETCH_AHEAD (QVX_CLAIM_AHEAD / 2)
 #endif
 #ifndef QVX_ISSUE_LANES
-#define QVX_ISSUE_LANES 2
+#define QVX_ISSUE_LANES 4
+#endif
+#ifndef QVX_BF16_PASSES
+#define QVX_BF16_PASSES 3   // bf16 pools: 3 = queries and probabilities as value + remainder, 1 = the queries only
+#endif
+#ifndef QVX_LAZY_RESCALE
+#define QVX_LAZY_RESCALE 1
+#endif
+#ifndef QVX_PF_DIST
+#define QVX_PF_DIST 0    // tiles the producer asks into the L2 ahead of the tile it copies into the ring (0: none)
+#endif
+constexpr uint32_t PF_DIST = QVX_PF_DIST;
+#ifndef QVX_PREFETCH_TILES
+#define QVX_PREFETCH_TILES 128   // tiles of a CTA's first item asked into the L2 while it waits for the launch before it (0: none)
 #endif
 constexpr uint32_t ISSUE_LANES = QVX_ISSUE_LANES;  // lanes of the producer warp that issue tiles side by side
 constexpr uint32_t CLAIM_AHEAD = QVX_CLAIM_AHEAD;  // tiles before an item's end at which the producer claims the next item
@@ -83,6 +99,7 @@ struct StreamArgs {
     uint64_t block_bytes;
     uint32_t page_bytes, tiles_per_block, heads, item_words, n_items, kv_out;
     uint32_t overlap;       // the pool and the tables do not depend on the work before this launch in the stream
+    uint32_t trace_id;      // the launch's number (experiment builds that trace; otherwise unused)
     float scale_log2;
 };
 
@@ -92,14 +109,31 @@ struct StreamArgs {
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-#ifdef QVX_TRACE
-// Experiment builds only: per-CTA timestamps of the kernel's phases, dumped by the host.
+// Per-CTA timestamps of the kernel's phases, for experiment builds (-DQVX_EXPERIMENTS -DQVX_TRACE): the host
+// dumps the marks of the QVX_TRACE_AT-th launch (every launch without it) to the file QVX_TRACE_FILE names.
+// Launches alternate between two buffers and tag their marks with their number, so a launch that overlaps
+// its neighbours can be told from them.  In every other build a Tracer is empty and its marks cost nothing.
+#if defined(QVX_EXPERIMENTS) && defined(QVX_TRACE)
+#define QVX_TRACING 1
 constexpr int TRACE_PER_CTA = 256;
-__device__ unsigned long long g_trace[512 * TRACE_PER_CTA];
-__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define TRACE(slot_var, tag) do { if ((slot_var) < TRACE_PER_CTA / 4) { g_trace[blockIdx.x * TRACE_PER_CTA + trace_base + (slot_var)] = (gtime() << 8) | (tag); (slot_var)++; } } while (0)
+__device__ unsigned long long g_trace[2][512 * TRACE_PER_CTA];
+struct Tracer {
+    uint32_t base, n = 0, id;
+    bool on;
+    __device__ __forceinline__ Tracer(uint32_t id, uint32_t quarter, bool on) : base(quarter * (TRACE_PER_CTA / 4)), id(id), on(on) {}
+    __device__ __forceinline__ void mark(uint32_t tag) {
+        if (!on || n >= TRACE_PER_CTA / 4) return;
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_trace[id & 1][blockIdx.x * TRACE_PER_CTA + base + n++] = (t << 12) | ((id & 15u) << 8) | tag;
+    }
+};
 #else
-#define TRACE(slot_var, tag) do { } while (0)
+#define QVX_TRACING 0
+struct Tracer {
+    __device__ __forceinline__ Tracer(uint32_t, uint32_t, bool) {}
+    __device__ __forceinline__ void mark(uint32_t) {}
+};
 #endif
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -136,11 +170,11 @@ struct StreamSmem {
     static constexpr uint32_t rec_off = q_off + q_bytes;
     static constexpr uint32_t bar_off = rec_off + rec_bytes;
     // full[stages], empty[stages], qfull[Q_SLOTS], qempty[Q_SLOTS], rec[REC_SLOTS],
-    // res_full[MAIL_SLOTS], res_free[MAIL_SLOTS], note[NOTE_SLOTS], then the abort word and the notes
+    // res_full[MAIL_SLOTS], res_free[MAIL_SLOTS], note[NOTE_SLOTS], then the notes
     static constexpr uint32_t n_bars = 2 * stages + 2 * Q_SLOTS + REC_SLOTS + 2 * MAIL_SLOTS + NOTE_SLOTS;
-    static constexpr uint32_t abort_off = bar_off + n_bars * 8;
-    static constexpr uint32_t mail_off = abort_off + 16;
-    static constexpr uint32_t total = mail_off + NOTE_SLOTS * 32;
+    static constexpr uint32_t mail_off = (bar_off + n_bars * 8 + 15u) & ~15u;
+    static constexpr uint32_t final_off = mail_off + NOTE_SLOTS * 32;  // chunks this CTA hands over in all, once its producer knows
+    static constexpr uint32_t total = final_off + 16;
 #if QVX_CW <= 4  // (experiment builds with more consumer warps only run the head sizes that fit)
     static_assert(stages >= CW, "the ring needs a stage per consumer warp");
 #endif
@@ -271,6 +305,44 @@ __device__ __forceinline__ void fold_range(Running<D>& r, const float* p0, uint3
     }
 }
 
+// The same fold with every entry's loads in flight at once: the entries are first copied into shared memory
+// at `stage` (cp.async: no register holds them meanwhile), then folded from there, in entry order.  One round
+// trip to the L2 instead of one per PAIR entries.  `stage` must hold (c1 - c0) entries of 8 * D + 16 floats
+// and be nobody else's: the epilogue warp uses the CTA's ring for it once the CTA has streamed its last tile.
+template <int D>
+__device__ __forceinline__ void fold_range_staged(Running<D>& r, const float* p0, uint32_t c0, uint32_t c1, uint32_t mine,
+                                                  const float4 (&E)[8 * D / 4 / 32], float Eml, uint32_t lane,
+                                                  uint8_t* stage_ptr, uint32_t stage) {
+    constexpr uint32_t PART_STRIDE = 8 * D + 16;
+    constexpr uint32_t PIECES = PART_STRIDE / 4;  // 16-byte pieces of an entry
+    constexpr int NJ = 8 * D / 4 / 32;
+    for (uint32_t c = c0; c < c1; c++) {
+        if (c == mine) continue;
+        const float* pe = p0 + (size_t)c * PART_STRIDE;
+        const uint32_t dst = stage + (c - c0) * PART_STRIDE * 4;
+        for (uint32_t i = lane; i < PIECES; i += 32) cp_async_16(dst + i * 16, pe + i * 4);
+    }
+    cp_async_wait_all();
+    __syncwarp();
+    for (uint32_t c = c0; c < c1; c++) {
+        const float* se = reinterpret_cast<const float*>(stage_ptr) + (size_t)(c - c0) * PART_STRIDE;
+        float ml = Eml;
+        if (c != mine && lane < 16) ml = se[8 * D + lane];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const uint32_t i = lane + j * 32, h = i / (D / 4);
+            const float4 v = c != mine ? *reinterpret_cast<const float4*>(se + h * D + (i % (D / 4)) * 4) : E[j];
+            const float m = __shfl_sync(0xffffffffu, ml, h), l = __shfl_sync(0xffffffffu, ml, 8 + h);
+            const float mn = fmaxf(r.M[j], m);
+            const float so = ex2(r.M[j] - mn), w = ex2(m - mn);
+            r.acc[j].x = fmaf(v.x, w, r.acc[j].x * so); r.acc[j].y = fmaf(v.y, w, r.acc[j].y * so);
+            r.acc[j].z = fmaf(v.z, w, r.acc[j].z * so); r.acc[j].w = fmaf(v.w, w, r.acc[j].w * so);
+            r.L[j] = fmaf(l, w, r.L[j] * so);
+            r.M[j] = mn;
+        }
+    }
+}
+
 // Release / acquire fences at device scope (__threadfence() is the sequentially consistent one).
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 
@@ -324,11 +396,7 @@ __device__ __forceinline__ bool fold_ahead(const StreamArgs& a, const Mail& it, 
 // merge keeps a running maximum, so an entry's maximum is needed only together with its values.
 template <int D>
 __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint32_t lane, float4 (&E)[8 * D / 4 / 32], float Eml,
-                                      bool ahead, Running<D>& r
-#ifdef QVX_TRACE
-                                      , uint32_t& tp, const uint32_t trace_base
-#endif
-) {
+                                      bool ahead, Running<D>& r, Tracer& tr, bool ring_free, uint8_t* stage_ptr, uint32_t stage) {
     constexpr uint32_t PART_STRIDE = 8 * D + 16;
     constexpr int NJ = 8 * D / 4 / 32;
     uint32_t hh[NJ], off[NJ];
@@ -349,9 +417,7 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
             uint32_t last = 0;
             if (lane == 0) last = atomicAdd(claimed, 1u) == size - 1 ? 1u : 0u;
             last = __shfl_sync(0xffffffffu, last, 0);
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, last ? 14 : 17);  // claim answered
-#endif
+            tr.mark(last ? 14 : 17);  // claim answered
             if (!last) {
                 float* pe = p0 + (size_t)mine * PART_STRIDE;
                 const uint64_t keep = l2_policy_evict_last();  // read again by the node's last arrival: stay in the L2
@@ -368,18 +434,21 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
                 if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
                 return;
             }
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, 15);  // the others' entries are published
-#endif
+            tr.mark(15);  // the others' entries are published
             fence_acq_rel_gpu();
             r.clear();
         }
         if (lane == 0) { *claimed = 0; *published = 0; }  // ready for the next launch
-        fold_range<D, (NJ <= 8 ? 2 : 1)>(r, p0, ahead ? mine : 0u, size, mine, E, Eml, lane);
+        // `ring_free`: the CTA has streamed its last tile and its ring (at `stage`) is free to stage the entries in.
+        if (ring_free && !ahead && size * PART_STRIDE * 4 <= StreamSmem<D>::stages * StreamSmem<D>::stage_bytes) {
+            tr.mark(26);  // staged fold begins
+            fold_range_staged<D>(r, p0, 0u, size, mine, E, Eml, lane, stage_ptr, stage);
+        } else {
+            tr.mark(27);  // fold from registers begins
+            fold_range<D, (NJ <= 8 ? 2 : 1)>(r, p0, ahead ? mine : 0u, size, mine, E, Eml, lane);
+        }
         ahead = false;
-#ifdef QVX_TRACE
-        if (lane == 0) TRACE(tp, 16);  // node merged
-#endif
+        tr.mark(16);  // node merged
         if (n <= MERGE_FAN) {
             // The root: the sequence's output.
 #pragma unroll
@@ -410,7 +479,7 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
     }
 }
 
-template <int DT, int D, bool PRECISE>
+template <int DT, int D, int PRECISE>
 __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) attn_stream_kernel(StreamArgs a) {
     using SM = StreamSmem<D>;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -419,8 +488,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     const uint32_t full0 = sbase + SM::bar_off, empty0 = full0 + SM::stages * 8;
     const uint32_t qfull0 = empty0 + SM::stages * 8, qempty0 = qfull0 + Q_SLOTS * 8, recbar0 = qempty0 + Q_SLOTS * 8;
     const uint32_t rfull0 = recbar0 + REC_SLOTS * 8, rfree0 = rfull0 + MAIL_SLOTS * 8, note0 = rfree0 + MAIL_SLOTS * 8;
-    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + SM::abort_off);
     volatile Mail* mailbox = reinterpret_cast<volatile Mail*>(smem + SM::mail_off);
+    volatile uint32_t* final_chunks = reinterpret_cast<volatile uint32_t*>(smem + SM::final_off);
 
     if (threadIdx.x == 0) grid_dep_launch();
     // Without the caller's word that the pool is settled, nothing is touched before the stream's
@@ -433,7 +502,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         for (uint32_t s = 0; s < REC_SLOTS; s++) mbar_init(recbar0 + s * 8, 1);
         for (uint32_t s = 0; s < MAIL_SLOTS; s++) { mbar_init(rfull0 + s * 8, CW); mbar_init(rfree0 + s * 8, 1); }
         for (uint32_t s = 0; s < NOTE_SLOTS; s++) mbar_init(note0 + s * 8, 1);
-        *abort_flag = 0;
+        *final_chunks = NO_PART;
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -463,6 +532,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         // pause.  So ISSUE_LANES lanes issue consecutive tiles in step (one instruction stream, a tile
         // each); everything per tile is derived with shifts and constants, nothing with a division.
         uint32_t nprod = 0;  // tiles issued before the current item, over all items
+        uint32_t nchunks = 0;  // chunks of the items up to the current one, over all items
         const bool one_copy = a.page_bytes == SM::tile_bytes;  // one tile per block: its values follow its keys
         const uint32_t tpb = a.tiles_per_block;
         const bool tpb_pow2 = (tpb & (tpb - 1u)) == 0u;
@@ -471,10 +541,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         // keeps coming back to (partial results, records, queries) stays there.
         const uint64_t stream_policy = l2_policy_evict_first();
         bool failed = false, queue_dry = false;
-#ifdef QVX_TRACE
-        const uint32_t trace_base = 0; uint32_t tp = 0;
-        if (lane == 0) TRACE(tp, 1);   // producer start
-#endif
+        Tracer tr(a.trace_id, 0, lane == 0);
+        tr.mark(1);  // producer start
         // The first item needs no atomic: CTA b starts with item b, the queue hands out the rest.
         if (lane == 0) fetch(0, blockIdx.x);
         for (uint32_t k = 0;; k++) {
@@ -484,9 +552,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             bool ok = mbar_wait(recbar0 + rslot * 8, (k / REC_SLOTS) & 1);
             ok = ok && mbar_wait(qempty0 + qslot * 8, ((k / Q_SLOTS) & 1) ^ 1);
             if (!__all_sync(0xffffffffu, ok)) { failed = true; break; }
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, 5);  // record and query slot ready
-#endif
+            tr.mark(5);  // record and query slot ready
             const uint32_t* rec = rec_base + rslot * REC_WORDS;
             const uint32_t seq = rec[0], tokens = rec[1], head0 = rec[2], nheads = rec[3] & 0xffffu, kvh = rec[3] >> 16;
             if (tokens == 0) {
@@ -495,6 +561,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
             const uint8_t* base = a.pool + (uint64_t)kvh * 2u * a.page_bytes;
             const uint32_t ntiles = (tokens + TILE - 1) / TILE;
+            nchunks += rec[9];
             const uint32_t* ids = rec + QVX_ITEM_HEADER_WORDS;
             auto issue_tile = [&](uint32_t tau) -> bool {  // any lane: tile `tau` of this item
                 const uint32_t n = nprod + tau;
@@ -513,8 +580,25 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 }
                 return true;
             };
+            // Asks the L2 for tile `tau` of this item; nothing waits for it.  The ring holds only what fits the shared
+            // memory, and half of it is being multiplied at any time: run ahead of it in the L2, where there is room,
+            // so that the device memory sees requests PF_DIST tiles deep and the ring only has to cover the L2's latency.
+            auto prefetch_tile = [&](uint32_t tau) {
+                const uint32_t bi = tpb_pow2 ? tau >> tpb_shift : tau / tpb, bj = tau - bi * tpb;
+                const uint8_t* src = base + (uint64_t)ids[bi] * a.block_bytes + bj * SM::tile_bytes;
+                if (one_copy) {
+                    bulk_prefetch_l2(src, SM::stage_bytes);
+                } else {
+                    bulk_prefetch_l2(src, SM::tile_bytes);
+                    bulk_prefetch_l2(src + a.page_bytes, SM::tile_bytes);
+                }
+            };
             const bool last_chunk = rec[4] == NO_PART || rec[4] - rec[5] + rec[9] == rec[6];  // the run ends the sequence
             uint32_t tau0 = 0;
+            if (PF_DIST > 0 && !(k == 0 && a.overlap)) {  // the item's head, a tile per lane (the first item of an overlapped launch: below)
+                const uint32_t upto = ntiles < PF_DIST ? ntiles : PF_DIST;
+                for (uint32_t tau = lane; tau < upto; tau += 32) prefetch_tile(tau);
+            }
             if (k == 0 && a.overlap) {
                 // The first item's old positions stream while the stream's earlier work finishes;
                 // a chunk that holds the step's new row waits, since its rows come from that work.
@@ -524,6 +608,16 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                         for (uint32_t tau = lane; tau < tau0; tau += ISSUE_LANES)
                             if (!issue_tile(tau)) { failed = true; break; }
                 }
+#if QVX_PREFETCH_TILES > 0
+                // The ring is full and nothing more can be asked for until the queries exist; the memory the
+                // draining launch before this one no longer uses is idle meanwhile.  The rest of this first
+                // item is asked into the L2 now (one request per tile and lane; nothing waits for them), so
+                // that its copies find it there once the launch proper begins.
+                {
+                    const uint32_t upto = ntiles < tau0 + QVX_PREFETCH_TILES ? ntiles : tau0 + QVX_PREFETCH_TILES;
+                    for (uint32_t tau = tau0 + lane; tau < upto; tau += 32) prefetch_tile(tau);
+                }
+#endif
                 grid_dep_wait();
             }
             if (a.k_new != nullptr) {
@@ -560,9 +654,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                          qfull0 + qslot * 8);
             }
             if (lane < ISSUE_LANES) {
-#ifdef QVX_TRACE
-                if (lane == 0) TRACE(tp, 2);  // item issue begins
-#endif
+                tr.mark(2);  // item issue begins
                 // Item k + 1 is claimed late: CLAIM_AHEAD tiles before this item's last tile is
                 // asked for, which is about the time its index and then its record take to come
                 // back.  A CTA so never sits on work that an idle CTA could take: the launch ends
@@ -580,6 +672,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     const uint32_t idx_next = asked ? gridDim.x + claimed : a.n_items;
                     fetch(k + 1, idx_next);
                     queue_dry = idx_next >= a.n_items;
+                    // The item being issued is this CTA's last: once its last chunk's states are handed over, nothing
+                    // is copied into the ring any more and the epilogue warp may use it.
+                    if (queue_dry) *final_chunks = nchunks;
                     fetched = true;
                 };
                 for (uint32_t t0 = tau0; t0 < ntiles && !failed; t0 += ISSUE_LANES) {
@@ -589,26 +684,20 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     }
                     const uint32_t tau = t0 + lane;
                     if (tau < ntiles && !issue_tile(tau)) failed = true;
+                    if (PF_DIST > 0 && tau + PF_DIST < ntiles) prefetch_tile(tau + PF_DIST);
                 }
                 if (lane == 0 && !fetched && !failed) {  // every tile went out before the dependency wait
                     if (!queue_dry) { claimed = atomicAdd(a.queue, 1u); asked = true; }
                     fetch_next();
                 }
-#ifdef QVX_TRACE
-                if (lane == 0) TRACE(tp, 3);  // item issue ends
-#endif
+                tr.mark(3);  // item issue ends
             }
             nprod += ntiles;
             if (__any_sync(0xffffffffu, failed)) { failed = true; break; }
         }
         if (lane == 0) {
-            if (failed) {
-                *abort_flag = 1;
-                atomicExch(a.status, STATUS_WAIT_TIMEOUT);
-            }
-#ifdef QVX_TRACE
-            TRACE(tp, 4);  // producer exit
-#endif
+            if (failed) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
+            tr.mark(4);  // producer exit
             // The last CTA to run out of work leaves the queue ready for the next launch.
             const uint32_t done = atomicAdd(a.queue + 1, 1u);
             if (done == gridDim.x - 1) { a.queue[0] = 0; a.queue[1] = 0; }
@@ -628,9 +717,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         if (a.overlap) grid_dep_wait();  // before this grid's first write to `out` or the scratch
         constexpr int NJ = 8 * D / 4 / 32;
         const float* res_all = reinterpret_cast<const float*>(smem + SM::res_off);
-#ifdef QVX_TRACE
-        const uint32_t trace_base = TRACE_PER_CTA / 4; uint32_t tp = 0;
-#endif
+        Tracer tr(a.trace_id, 1, lane == 0);
         Running<D> run;
         for (uint32_t kp = 0;; kp++) {
             const uint32_t ms = kp % MAIL_SLOTS, ns = kp % NOTE_SLOTS;
@@ -641,14 +728,19 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             m.nch = mailbox[ns].nch; m.counter = mailbox[ns].counter; m.stop = mailbox[ns].stop; m.chunk = mailbox[ns].chunk;
             if (m.stop) return;
             // While they stream it: if the item is its node's last arrival, fold what precedes it.
-            const bool ahead = m.chunk != NO_PART && fold_ahead<D>(a, m, lane, run);
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, ahead ? 18 : 19);  // note read (and the node's other entries folded)
-#endif
+            bool ahead = m.chunk != NO_PART && fold_ahead<D>(a, m, lane, run);
+            if (m.chunk != NO_PART && !ahead && merge_node_of(m.chunk, m.nch).size >= 2) {
+                // Not yet: some other chunk of the node has not arrived.  This warp has nothing else to do until the
+                // item's states are ready, so it looks again (a round trip to the L2 each time) in between.
+                for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+                    const uint32_t ready = mbar_try_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1) ? 1u : 0u;
+                    if (__shfl_sync(0xffffffffu, ready, 0)) break;
+                    if ((ahead = fold_ahead<D>(a, m, lane, run))) break;
+                }
+            }
+            tr.mark(ahead ? 18 : 19);  // note read (and the node's other entries folded)
             if (!__all_sync(0xffffffffu, mbar_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, 10);  // states ready
-#endif
+            tr.mark(10);  // states ready
             const bool direct = m.chunk == NO_PART;
             const float* rb = res_all + ms * CW * SM::res_floats;
             // Output i = lane + 32 j of the item's 8 x D/4 float4 values, over the CW states in
@@ -691,9 +783,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
             __syncwarp();  // every lane has read what it needs of the buffer
             if (lane == 0) mbar_arrive(rfree0 + ms * 8);
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, 13);  // states merged, buffer given back
-#endif
+            tr.mark(13);  // states merged, buffer given back
             if (direct) {
 #pragma unroll
                 for (int j = 0; j < NJ; j++) {
@@ -705,15 +795,11 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     }
                 }
             } else {
-#ifdef QVX_TRACE
-                climb<D>(a, m, lane, E, Eml, ahead, run, tp, trace_base);
-#else
-                climb<D>(a, m, lane, E, Eml, ahead, run);
-#endif
+                // The CTA's last chunk: its states are in, so every copy into the ring has landed and been read.
+                const bool ring_free = kp + 1 == *final_chunks;
+                climb<D>(a, m, lane, E, Eml, ahead, run, tr, ring_free, smem + SM::ring_off, sbase + SM::ring_off);
             }
-#ifdef QVX_TRACE
-            if (lane == 0) TRACE(tp, 11);  // deliver done
-#endif
+            tr.mark(11);  // deliver done
         }
     }
 
@@ -724,12 +810,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     const uint32_t v_row = r8 + 8 * (mid >> 1), v_chunk = mid & 1;  // values: A = V^T (ldmatrix.trans)
     float* res_all = reinterpret_cast<float*>(smem + SM::res_off);
     uint32_t nbase = 0;   // tiles of the items before this one
-#ifdef QVX_TRACE
-    const uint32_t trace_base = TRACE_PER_CTA / 2 + (warp == 0 ? 0 : TRACE_PER_CTA / 4); uint32_t tp = 0;
-    const bool tr = lane == 0 && (warp == 0 || warp == CW - 1);
-#endif
+    Tracer tr(a.trace_id, warp == 0 ? 2 : 3, lane == 0 && (warp == 0 || warp == CW - 1));
     bool dead = false;    // this warp gave up a wait
     uint32_t kc = 0;      // chunks handed over so far, over all items
+    // The queries come from the stream's earlier work, which the producer waits for before it asks for
+    // them: wait for it here too (it returns when that work is done, however long it takes), so that the
+    // bounded wait below only ever measures this CTA's own copies.
+    if (a.overlap) grid_dep_wait();
     for (uint32_t k = 0;; k++) {
         const uint32_t rslot = k % REC_SLOTS, qslot = k % Q_SLOTS;
         Item it{};
@@ -745,7 +832,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         }
         if (dead) {
             // Every other wait in the CTA is bounded too: the others give up in their turn.
-            *abort_flag = 1;
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
         }
@@ -760,9 +846,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
             return;
         }
-#ifdef QVX_TRACE
-        if (tr) TRACE(tp, 20);  // item header read
-#endif
+        tr.mark(20);  // item header read
         // Q^T fragments (the B operand), once per item: this lane holds head g, dims 16*ks + 2t + {0,1,8,9}.
         uint32_t qf[D / 16][2], ql[D / 16][2];
         {
@@ -814,7 +898,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 if (!__all_sync(0xffffffffu, mbar_wait(full0 + st * 8, ph))) { dead = true; break; }
                 const uint32_t kt = sbase + SM::ring_off + st * SM::stage_bytes, vt = kt + SM::tile_bytes;
                 const uint32_t valid = min((uint32_t)TILE, ctokens - tau * TILE);
-#ifndef QVX_EXPERIMENT_NOCOMPUTE
+#if !(defined(QVX_EXPERIMENTS) && defined(QVX_EXPERIMENT_NOCOMPUTE))
                 // S^T = K Q^T; the value pass and the remainder pass accumulate separately so the
                 // chain of dependent tensor-core ops is half as long.
                 float sc[4] = {0.f, 0.f, 0.f, 0.f}, sr[4] = {0.f, 0.f, 0.f, 0.f};
@@ -823,9 +907,9 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                     uint32_t af[4];
                     ldmatrix_x4(kt + k_row * (D * 2) + (((2 * ks + k_chunk) ^ (k_row & 7)) << 4), af);
                     mma_16816<DT>(sc, af, qf[ks][0], qf[ks][1]);
-                    if constexpr (PRECISE) mma_16816<DT>(sr, af, ql[ks][0], ql[ks][1]);
+                    if constexpr (PRECISE & 1) mma_16816<DT>(sr, af, ql[ks][0], ql[ks][1]);
                 }
-                if constexpr (PRECISE) { sc[0] += sr[0]; sc[1] += sr[1]; sc[2] += sr[2]; sc[3] += sr[3]; }
+                if constexpr (PRECISE & 1) { sc[0] += sr[0]; sc[1] += sr[1]; sc[2] += sr[2]; sc[3] += sr[3]; }
                 if (valid < TILE) {
                     // The tail of the last block: unwritten slots hold whatever the pool held before.
                     if (g >= valid) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
@@ -857,15 +941,18 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 split16<DT>(p2, p3, ph1, pl1);
                 const uint32_t pb0 = movmatrix_trans(ph0), pb1 = movmatrix_trans(ph1);
                 uint32_t pc0 = 0, pc1 = 0;
-                if constexpr (PRECISE) { pc0 = movmatrix_trans(pl0); pc1 = movmatrix_trans(pl1); }
+                if constexpr (PRECISE & 2) { pc0 = movmatrix_trans(pl0); pc1 = movmatrix_trans(pl1); }
                 // O^T = O^T * alpha + V^T P^T
+                // The running maxima settle after a sequence's first tiles: when no lane's moved, every factor is 1
+                // and the multiplications below are left out (x * 1.0f is x: the bits are the same either way).
+                const bool rescale = QVX_LAZY_RESCALE ? __any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f) : true;
 #pragma unroll
                 for (int mt = 0; mt < D / 16; mt++) {
-                    o[mt][0] *= al0; o[mt][1] *= al1; o[mt][2] *= al0; o[mt][3] *= al1;
+                    if (rescale) { o[mt][0] *= al0; o[mt][1] *= al1; o[mt][2] *= al0; o[mt][3] *= al1; }
                     uint32_t vf[4];
                     ldmatrix_x4_trans(vt + v_row * (D * 2) + (((2 * mt + v_chunk) ^ (v_row & 7)) << 4), vf);
                     mma_16816<DT>(o[mt], vf, pb0, pb1);
-                    if constexpr (PRECISE) mma_16816<DT>(o[mt], vf, pc0, pc1);
+                    if constexpr (PRECISE & 2) mma_16816<DT>(o[mt], vf, pc0, pc1);
                 }
 #else
                 (void)kt; (void)vt; (void)valid; (void)k_row; (void)k_chunk; (void)v_row; (void)v_chunk;
@@ -875,9 +962,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             }
             nbase += ntiles;
         }
-#ifdef QVX_TRACE
-        if (tr) TRACE(tp, 21);  // tiles done
-#endif
+        tr.mark(21);  // tiles done
         // Row sums over the positions held by the other lanes of the same t.
 #pragma unroll
         for (int sh = 4; sh <= 16; sh <<= 1) {
@@ -885,14 +970,12 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
         }
         if (dead) {
-            *abort_flag = 1;
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
         }
         // ---- this warp's state goes to the epilogue warp, and the warp goes on -------------------
         // The buffer is free once the epilogue warp has merged the item two before this one.
         if (!__all_sync(0xffffffffu, mbar_wait(rfree0 + ms * 8, ((kc / MAIL_SLOTS) & 1) ^ 1))) {
-            *abort_flag = 1;
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
         }
@@ -910,9 +993,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(rfull0 + ms * 8);
-#ifdef QVX_TRACE
-        if (tr) TRACE(tp, 23);  // state handed over
-#endif
+        tr.mark(23);  // state handed over
         }  // chunks of the item
     }
 }
@@ -932,7 +1013,7 @@ size_t attn_stream_partial_floats(uint32_t d) { return 8 * (size_t)d + 16; }
 uint32_t attn_stream_parts(uint32_t nch) { return merge_entries_total(nch); }
 uint32_t attn_stream_counters(uint32_t nch) { return merge_counters_total(nch); }
 
-template <int DT, int D, bool PRECISE>
+template <int DT, int D, int PRECISE>
 static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t s) {
     auto kernel = attn_stream_kernel<DT, D, PRECISE>;
     static int per_device[64] = {};  // set up once per device (the attribute belongs to the device's context)
@@ -951,18 +1032,21 @@ static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = a.overlap ? 1 : 0;
-#ifdef QVX_TRACE
+#if QVX_TRACING
     {
-        cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
+        static uint32_t launches = 0;
+        StreamArgs at = a;
+        at.trace_id = launches++;
         const char* path = getenv("QVX_TRACE_FILE");
-        if (e == cudaSuccess && path) {
+        const char* only = getenv("QVX_TRACE_AT");
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, at);
+        if (e == cudaSuccess && path && (!only || (uint32_t)atol(only) == launches)) {
             cudaDeviceSynchronize();
-            std::vector<unsigned long long> h(512 * TRACE_PER_CTA);
-            cudaMemcpyFromSymbol(h.data(), g_trace, h.size() * 8);
+            std::vector<unsigned long long> h(2 * 512 * TRACE_PER_CTA);  // this launch's buffer first, then the one before it
+            cudaMemcpyFromSymbol(h.data(), g_trace, h.size() * 4, (at.trace_id & 1) * h.size() * 4);
+            cudaMemcpyFromSymbol(h.data() + h.size() / 2, g_trace, h.size() * 4, ((at.trace_id & 1) ^ 1) * h.size() * 4);
             FILE* f = fopen(path, "wb");
-            if (f) { unsigned g2 = grid; fwrite(&g2, 4, 1, f); fwrite(h.data(), 8, h.size(), f); fclose(f); }
-            cudaMemset(nullptr, 0, 0);
-            void* sym = nullptr; cudaGetSymbolAddress(&sym, g_trace); cudaMemset(sym, 0, h.size() * 8);
+            if (f) { unsigned hdr[2] = {grid, at.trace_id & 15u}; fwrite(hdr, 4, 2, f); fwrite(h.data(), 8, h.size(), f); fclose(f); }
         }
         return check_cuda(dev, e, "streaming attention launch");
     }
@@ -989,15 +1073,30 @@ int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, con
     a.block_bytes = L.block_bytes; a.page_bytes = L.page_bytes; a.tiles_per_block = L.B / TILE;
     a.heads = (uint32_t)t->heads; a.item_words = t->item_words; a.n_items = (uint32_t)t->n_items;
     a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;
-    static const bool one_pass = getenv("QVX_ATTN_ONE_PASS") != nullptr;  // experiments only
-    const bool precise = L.dtype == QVX_BF16 && !one_pass;
+    a.trace_id = 0;
+    // bf16 carries 8 mantissa bits: the queries and the probabilities go through the tensor cores as a value and
+    // a remainder (bit 0: queries, bit 1: probabilities).  An experiment build can leave passes out
+    // (QVX_ATTN_ONE_PASS = 1: both, 2: the probabilities', 3: the queries').
+    int passes = L.dtype == QVX_BF16 ? QVX_BF16_PASSES : 0;
+#ifdef QVX_EXPERIMENTS
+    if (const char* v = getenv("QVX_ATTN_ONE_PASS")) {
+        const long n = atol(v);
+        if (L.dtype == QVX_BF16) passes = n == 1 ? 0 : n == 2 ? 1 : n == 3 ? 2 : 3;
+    }
+#endif
     LaunchTimer timer(dev, QVX_K_ATTN, s);
     int32_t rc = QVX_ERR_UNSUPPORTED;
 #define QVX_STREAM_CASE(TT, DD, PP) \
-    if (L.dtype == TT && L.d == DD && precise == PP) rc = launch_stream<TT, DD, PP>(dev, a, s);
-    QVX_STREAM_CASE(QVX_BF16, 64, true) QVX_STREAM_CASE(QVX_BF16, 128, true) QVX_STREAM_CASE(QVX_BF16, 256, true)
-    QVX_STREAM_CASE(QVX_BF16, 128, false)
-    QVX_STREAM_CASE(QVX_F16, 64, false) QVX_STREAM_CASE(QVX_F16, 128, false) QVX_STREAM_CASE(QVX_F16, 256, false)
+    if (L.dtype == TT && L.d == DD && passes == PP) rc = launch_stream<TT, DD, PP>(dev, a, s);
+    QVX_STREAM_CASE(QVX_BF16, 64, QVX_BF16_PASSES) QVX_STREAM_CASE(QVX_BF16, 128, QVX_BF16_PASSES)
+    QVX_STREAM_CASE(QVX_BF16, 256, QVX_BF16_PASSES)
+#ifdef QVX_EXPERIMENTS
+    if (L.d == 128 && passes != QVX_BF16_PASSES) {
+        QVX_STREAM_CASE(QVX_BF16, 128, 0) QVX_STREAM_CASE(QVX_BF16, 128, 1) QVX_STREAM_CASE(QVX_BF16, 128, 2)
+        QVX_STREAM_CASE(QVX_BF16, 128, 3)
+    }
+#endif
+    QVX_STREAM_CASE(QVX_F16, 64, 0) QVX_STREAM_CASE(QVX_F16, 128, 0) QVX_STREAM_CASE(QVX_F16, 256, 0)
 #undef QVX_STREAM_CASE
     if (rc == QVX_ERR_UNSUPPORTED) return fail(dev, rc, "streaming attention: no kernel for this geometry");
     return rc;

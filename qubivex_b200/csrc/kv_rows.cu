@@ -11,6 +11,12 @@
 // Algorithmic bytes per row pair: 2 * kv_out * (4 + e).
 // Reference layout: keys are dimension-major inside a block, a stride-B scatter of single
 // elements; one thread per element (compatibility path, not the fast one).
+//
+// The block ids come from device memory the host of the device-pointer entry points has not seen:
+// a row whose block lies at or past `pool_blocks` is skipped (nothing of it is written) and the
+// device's status word gets STATUS_BLOCK_OUT_OF_POOL, which the host reports at its next wait.
+#include <algorithm>
+
 #include "qvx_common.cuh"
 
 namespace qvx {
@@ -26,6 +32,8 @@ struct RowArgs {
     const uint32_t* blocks;
     const uint32_t* table_at;
     uint32_t n;
+    uint32_t pool_blocks;       // blocks the pool holds: a row for a block at or past it is skipped
+    int* status;                // the device's status word
 };
 
 __device__ __forceinline__ bool row_target(const RowArgs& a, uint32_t r, uint32_t& block, uint32_t& slot) {
@@ -38,6 +46,10 @@ __device__ __forceinline__ bool row_target(const RowArgs& a, uint32_t r, uint32_
         block = a.blocks[a.table_at[r] + p / a.L.B];
         slot = p % a.L.B;
     }
+    if (block >= a.pool_blocks) {
+        atomicExch(a.status, STATUS_BLOCK_OUT_OF_POOL);
+        return false;
+    }
     return true;
 }
 
@@ -45,6 +57,7 @@ __device__ __forceinline__ bool row_target(const RowArgs& a, uint32_t r, uint32_
 // blockIdx.y picks a group of NATIVE_GROUP rows, so a thread's index inside the group fits 32 bits
 // and is split with 32-bit divisions.
 constexpr uint32_t NATIVE_GROUP = 1024;
+constexpr uint32_t OUT_OF_POOL = 0xfffffffeu;  // in place of a pool position: the row's block id is not the pool's
 constexpr uint32_t NATIVE_PER_THREAD = 2;  // chunks per thread: all their loads are issued before anything waits
 __global__ void __launch_bounds__(256) kv_rows_native_kernel(RowArgs a) {
     const uint32_t cpr = a.L.row_bytes >> 4;  // chunks per row
@@ -75,14 +88,19 @@ __global__ void __launch_bounds__(256) kv_rows_native_kernel(RowArgs a) {
         if (a.at_direct) {
             at[u] = a.at_direct[r];
         } else {
-            const uint32_t p = a.pos[r];
-            at[u] = a.blocks[a.table_at[r] + p / a.L.B] * a.L.B + p % a.L.B;
+            const uint32_t p = a.pos[r], blk = a.blocks[a.table_at[r] + p / a.L.B];
+            // (checked before the multiplication: a wild id must not wrap into the pool)
+            at[u] = blk < a.pool_blocks ? blk * a.L.B + p % a.L.B : OUT_OF_POOL;
         }
     }
 #pragma unroll
     for (uint32_t u = 0; u < NATIVE_PER_THREAD; u++) {
         if (at[u] == 0xffffffffu) continue;
         const uint32_t block = at[u] / a.L.B, slot = at[u] % a.L.B, w = ww[u];
+        if (at[u] == OUT_OF_POOL || block >= a.pool_blocks) {  // not this pool's block: the row is skipped, the host told
+            atomicExch(a.status, STATUS_BLOCK_OUT_OF_POOL);
+            continue;
+        }
         const uint32_t g = pow2 ? w >> (cpr_shift + 1u) : w / (2u * cpr), kv = (pow2 ? w >> cpr_shift : w / cpr) & 1u,
                        c = pow2 ? w & (cpr - 1u) : w % cpr;
         uint4 out;
@@ -116,13 +134,16 @@ __global__ void __launch_bounds__(256) kv_rows_element_kernel(RowArgs a) {
     else *reinterpret_cast<uint16_t*>(dst) = narrow16(x, a.L.dtype);
 }
 
+extern int* device_status_word(qvx_device* dev);
+
 int32_t launch_kv_rows(qvx_device* dev, const Layout& L, void* pool, const float* k_rows,
                        const float* v_rows, size_t row_stride_f32, const uint32_t* at_direct,
                        const uint32_t* pos, const uint32_t* blocks, const uint32_t* table_at, size_t n,
-                       int kind, cudaStream_t s) {
+                       size_t pool_blocks, int kind, cudaStream_t s) {
     if (n == 0) return QVX_OK;
     if (n > 0x7fffffffu) return fail(dev, QVX_ERR_CORE, "kv rows: %zu rows do not fit 31 bits", n);
-    RowArgs a{L, (uint8_t*)pool, k_rows, v_rows, row_stride_f32, at_direct, pos, blocks, table_at, (uint32_t)n};
+    RowArgs a{L, (uint8_t*)pool, k_rows, v_rows, row_stride_f32, at_direct, pos, blocks, table_at, (uint32_t)n,
+              (uint32_t)std::min<size_t>(pool_blocks, 0xffffffffu), device_status_word(dev)};
     LaunchTimer timer(dev, kind, s);
     bool aligned = (((uintptr_t)k_rows | (uintptr_t)v_rows | (uintptr_t)pool) & 15u) == 0 &&
                    (row_stride_f32 * 4) % 16 == 0;

@@ -117,8 +117,10 @@ static int32_t check_status(qvx_device* dev) {
         cudaMemset(dev->counters, 0, 2 * dev->counters_cap * 4);
         if (dev->queue) cudaMemset(dev->queue, 0, 16);
     }
-    return fail(dev, QVX_ERR_DEVICE, "cuda device error: %s (status %d); the op's outputs are not valid",
-                st == 2 ? "a position beyond the bound the caller gave" : "a kernel gave up a bounded wait", st);
+    const char* what = st == STATUS_POSITION_BOUND      ? "a position beyond the bound the caller gave"
+                       : st == STATUS_BLOCK_OUT_OF_POOL ? "a block id at or past pool_blocks (that row or move was skipped)"
+                                                        : "a kernel gave up a bounded wait";
+    return fail(dev, QVX_ERR_DEVICE, "cuda device error: %s (status %d); the op's outputs are not valid", what, st);
 }
 
 // ---- capacity accounting, as SimDevice::reserve (sim.rs:176-203) -----------------------------
@@ -254,25 +256,25 @@ static int32_t take_slice(qvx_device* dev, DeviceExtras* x, size_t need, size_t*
 // constants only (never of the batch or the device), so its result is the same whatever shares
 // the op.  512 positions, doubled (to at most 2048) while the sequence would still make more
 // than 32 chunks: long contexts get fewer, larger items and a shallower merge tree.
-// QVX_CHUNK_TOKENS fixes the size instead (experiments).
+// These constants fix the bits of every result (a chunk is the unit of the online softmax), so the
+// shipped library reads them from nowhere; an experiment build (-DQVX_EXPERIMENTS) takes them from the
+// environment: QVX_CHUNK_TOKENS (a fixed size), QVX_CHUNK_BASE, QVX_CHUNK_MOST.
+#ifdef QVX_EXPERIMENTS
+static uint32_t env_u32(const char* name, uint32_t otherwise) {
+    const char* v = getenv(name);
+    const long n = v ? atol(v) : 0;
+    return n > 0 ? (uint32_t)n : otherwise;
+}
+#endif
 static uint32_t chunk_tokens_for(const Layout& L, uint32_t len) {
-    static const uint32_t configured = [] {
-        const char* v = getenv("QVX_CHUNK_TOKENS");
-        long n = v ? atol(v) : 0;
-        return (uint32_t)(n > 0 ? n : 0);
-    }();
-    static const uint32_t base = [] {  // experiments: the size the doubling starts from
-        const char* v = getenv("QVX_CHUNK_BASE");
-        long n = v ? atol(v) : 0;
-        return (uint32_t)(n > 0 ? n : 512);
-    }();
+#ifdef QVX_EXPERIMENTS
+    static const uint32_t configured = env_u32("QVX_CHUNK_TOKENS", 0), base = env_u32("QVX_CHUNK_BASE", 512),
+                          most = env_u32("QVX_CHUNK_MOST", 32);
+#else
+    constexpr uint32_t configured = 0, base = 512, most = 32;
+#endif
     uint32_t c = std::max(configured ? configured : base, L.B) / L.B * L.B;
     while (c > 2048 && c > L.B) c -= L.B;
-    static const uint32_t most = [] {  // experiments: the chunk count beyond which the size doubles
-        const char* v = getenv("QVX_CHUNK_MOST");
-        long n = v ? atol(v) : 0;
-        return (uint32_t)(n > 0 ? n : 32);
-    }();
     if (!configured)
         while ((len + c - 1) / c > most && c * 2 <= 2048) c *= 2;
     return c;
@@ -285,10 +287,19 @@ static uint32_t chunk_tokens_for(const Layout& L, uint32_t len) {
 // less often; with few, items stay single chunks and the queue evens the CTAs out.  A run never
 // exceeds RUN_TOKENS positions (its block ids ride in the item's record).
 static const uint32_t RUN_TOKENS = 2048;
+#ifndef QVX_SMALL_TOKENS_DEFAULT
+#define QVX_SMALL_TOKENS_DEFAULT 256
+#endif
+// An experiment build reads a fixed run length from QVX_RUN_CHUNKS at every op (the tests that show
+// that the run length moves no bit use it); the shipped library always chooses by the rule below.
 static uint32_t run_chunks_override() {
-    const char* v = getenv("QVX_RUN_CHUNKS");  // experiments and tests: a fixed run length (read at every op)
+#ifdef QVX_EXPERIMENTS
+    const char* v = getenv("QVX_RUN_CHUNKS");
     const long n = v ? atol(v) : 0;
     return n > 0 ? (uint32_t)n : 0u;
+#else
+    return 0u;
+#endif
 }
 static uint32_t run_chunks_for(size_t total_chunks, uint32_t resident_ctas) {
     if (const uint32_t configured = run_chunks_override()) return configured;
@@ -301,7 +312,7 @@ static uint32_t run_chunks_for(size_t total_chunks, uint32_t resident_ctas) {
 constexpr size_t MAX_CHUNKS = 1000;
 static int32_t too_many_chunks(qvx_device* dev, size_t nch) {
     return fail(dev, QVX_ERR_UNSUPPORTED,
-                "cuda backend splits a context into at most %zu chunks, this one needs %zu: raise QVX_CHUNK_TOKENS",
+                "cuda backend splits a context into at most %zu chunks, this one needs %zu",
                 MAX_CHUNKS, nch);
 }
 
@@ -366,14 +377,31 @@ static void image_offsets(TableImage& im, size_t s, size_t n_blocks) {
 // `run` chunks from the front; the last `tail` chunks stay single, so that the end of the launch
 // has small items to even the CTAs out with.  Calls f(first chunk, chunks).
 static uint32_t run_tail_chunks() {
-    const char* v = getenv("QVX_RUN_TAIL");  // experiments
+#ifdef QVX_EXPERIMENTS
+    const char* v = getenv("QVX_RUN_TAIL");
     return v ? (uint32_t)atol(v) : 0u;
+#else
+    return 0u;
+#endif
 }
 template <typename F>
 static void for_each_run(uint32_t nch, uint32_t run, uint32_t tail, F f) {
     const uint32_t singles = run > 1 ? std::min(nch, tail) : 0u, front = nch - singles;
     for (uint32_t c = 0; c < front; c += run) f(c, std::min(run, front - c));
     for (uint32_t c = front; c < nch; c++) f(c, 1u);
+}
+
+// Where the short work items go in the queue: items of fewer than `small_tokens` positions are taken
+// out of the longest-first order and dealt out after the first `small_after` x (resident CTAs) items.
+// The order changes no bit of any result (a chunk's arithmetic does not depend on when it runs).
+struct QueueOrder { uint32_t small_tokens, small_after; };
+static QueueOrder queue_order() {
+    QueueOrder qo{QVX_SMALL_TOKENS_DEFAULT, 0};
+#ifdef QVX_EXPERIMENTS
+    if (const char* v = getenv("QVX_SMALL_TOKENS")) qo.small_tokens = (uint32_t)atol(v);
+    if (const char* v = getenv("QVX_SMALL_AFTER")) qo.small_after = (uint32_t)atol(v);
+#endif
+    return qo;
 }
 
 // CTAs of the streaming attention kernel the device keeps resident for this geometry; 0 when another
@@ -480,6 +508,23 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     for (uint32_t v = 0; v <= max_chunk; v++) start[v + 1] += start[v];
     std::vector<uint32_t> order(keys.size());
     for (uint32_t i = 0; i < keys.size(); i++) order[start[max_chunk - keys[i].tokens]++] = i;
+    // The short items do not go last.  Nearly every short item is a sequence's last, partly filled chunk,
+    // and whichever chunk of a sequence finishes last merges the others' results: at the very end of
+    // the queue that merge (a few rounds of loads) lasts longer than the item itself and every CTA's exit
+    // waits for one.  Dealt out first instead (or after the first `small_after` x CTAs items), the short ones
+    // are finished while every CTA still streams, the queue ends with long items -- which fold the others'
+    // results while they stream -- and the CTAs run dry within a fraction of a long item of one another.
+    const QueueOrder qo = queue_order();
+    if (ctas && qo.small_tokens) {
+        const size_t front = std::min<size_t>((size_t)qo.small_after * ctas, order.size());
+        std::vector<uint32_t> small, rest;
+        for (size_t n = front; n < order.size(); n++)
+            (keys[order[n]].tokens < qo.small_tokens ? small : rest).push_back(order[n]);
+        if (rest.size() >= ctas) {  // (with fewer long items than CTAs there is no long tail to end on)
+            std::copy(small.begin(), small.end(), order.begin() + front);
+            std::copy(rest.begin(), rest.end(), order.begin() + front + small.size());
+        }
+    }
     uint32_t* items = (uint32_t*)(img + im.off_items);
     for (size_t n = 0; n < keys.size(); n++) {
         const Key& k = keys[order[n]];
@@ -559,7 +604,7 @@ static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, c
     const bool fused = split && k_new && attn_split_fuses_append(t->L, t->heads);
     if (k_new && !fused) {
         int32_t rc = launch_kv_rows(dev, t->L, const_cast<void*>(pool), k_new, v_new, (size_t)t->L.kvh * t->L.d, nullptr, t->d_pos,
-                                    t->d_blocks, t->d_table_at, t->s, QVX_K_APPEND, s);
+                                    t->d_blocks, t->d_table_at, t->s, t->pool_blocks, QVX_K_APPEND, s);
         if (rc) return rc;
     }
     if (!split) return launch_attn_exact(dev, t, pool, q, out, s);
@@ -797,13 +842,12 @@ int32_t qvx_kv_sync(qvx_device* dev, const qvx_geometry* geo, void* pool, size_t
                     const uint32_t* sync_to, size_t n, void* stream) {
     if (!dev) return QVX_ERR_SHAPE;
     if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
-    (void)pool_blocks;
     std::lock_guard<std::mutex> lk(dev->mu);
     cudaSetDevice(dev->ordinal);
     Layout L = make_layout(geo);
     size_t kv_out = (size_t)L.kvh * L.d;
     return launch_kv_rows(dev, L, pool, rows, rows + kv_out, 2 * kv_out, sync_to, nullptr, nullptr, nullptr, n,
-                          QVX_K_SYNC, (cudaStream_t)stream);
+                          pool_blocks, QVX_K_SYNC, (cudaStream_t)stream);
 }
 
 int32_t qvx_kv_append(qvx_device* dev, const qvx_geometry* geo, void* pool, size_t pool_blocks, const float* k_new,
@@ -811,13 +855,12 @@ int32_t qvx_kv_append(qvx_device* dev, const qvx_geometry* geo, void* pool, size
                       size_t s, void* stream) {
     if (!dev) return QVX_ERR_SHAPE;
     if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
-    (void)pool_blocks;
     std::lock_guard<std::mutex> lk(dev->mu);
     cudaSetDevice(dev->ordinal);
     Layout L = make_layout(geo);
     size_t kv_out = (size_t)L.kvh * L.d;
-    return launch_kv_rows(dev, L, pool, k_new, v_new, kv_out, nullptr, pos, blocks, table_at, s, QVX_K_APPEND,
-                          (cudaStream_t)stream);
+    return launch_kv_rows(dev, L, pool, k_new, v_new, kv_out, nullptr, pos, blocks, table_at, s, pool_blocks,
+                          QVX_K_APPEND, (cudaStream_t)stream);
 }
 
 int32_t qvx_tables_create(qvx_device* dev, const qvx_geometry* geo, size_t pool_blocks, size_t heads, size_t s,
@@ -884,10 +927,9 @@ int32_t qvx_block_copy(qvx_device* dev, const qvx_geometry* geo, void* pool, siz
                        const uint32_t* dst, size_t n, void* stream) {
     if (!dev) return QVX_ERR_SHAPE;
     if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
-    (void)pool_blocks;
     std::lock_guard<std::mutex> lk(dev->mu);
     cudaSetDevice(dev->ordinal);
-    return launch_block_copy(dev, make_layout(geo), pool, src, dst, n, (cudaStream_t)stream);
+    return launch_block_copy(dev, make_layout(geo), pool, src, dst, n, pool_blocks, (cudaStream_t)stream);
 }
 
 // ---- the op with host memory ----------------------------------------------------------------------
@@ -1009,7 +1051,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     // sync rows, then the new rows, then attention: sim.rs:385-429.
     const float* d_sync = (const float*)(ds + o_sync);
     rc = launch_kv_rows(dev, L, pool->ptr, d_sync, d_sync + kv_out, 2 * kv_out, (const uint32_t*)(ds + o_syncto), nullptr,
-                        nullptr, nullptr, n_sync, QVX_K_SYNC, cs);
+                        nullptr, nullptr, n_sync, held, QVX_K_SYNC, cs);
     if (rc == QVX_OK && s)
         rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), (float*)(ds + o_out), variant, cs,
                            (const float*)(ds + o_k), (const float*)(ds + o_v));
@@ -1121,7 +1163,7 @@ int32_t qvx_block_copy_host(qvx_device* dev, qvx_buffer* pool, const qvx_geometr
     if (e != cudaSuccess) return check_cuda(dev, e, "block copy lists");
     e = cudaMemcpyAsync(d, src, 4 * n, cudaMemcpyHostToDevice, dev->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(d + n, dst, 4 * n, cudaMemcpyHostToDevice, dev->stream);
-    rc = e == cudaSuccess ? launch_block_copy(dev, L, pool->ptr, d, d + n, n, dev->stream) : check_cuda(dev, e, "block copy lists");
+    rc = e == cudaSuccess ? launch_block_copy(dev, L, pool->ptr, d, d + n, n, held, dev->stream) : check_cuda(dev, e, "block copy lists");
     cudaStreamSynchronize(dev->stream);
     cudaFree(d);
     dev->xfer.submissions++;

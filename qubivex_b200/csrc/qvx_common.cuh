@@ -19,6 +19,12 @@
 
 namespace qvx {
 
+// Values a kernel can leave in the device's status word (0 = fine).  The host reads the word at
+// its next wait on the device; the word is sticky until then.
+constexpr int STATUS_WAIT_TIMEOUT = 1;      // a bounded wait (mbarrier, published entries) ran out
+constexpr int STATUS_POSITION_BOUND = 2;    // a position beyond the bound the caller gave (qvx_attn_decode_static)
+constexpr int STATUS_BLOCK_OUT_OF_POOL = 3; // a block id >= pool_blocks: that row or move was skipped, nothing written
+
 // ---- geometry ------------------------------------------------------------------------
 QVX_HD uint32_t elem_size(uint32_t dtype) { return dtype == QVX_F32 ? 4u : 2u; }
 
@@ -193,11 +199,11 @@ struct LaunchTimer {
 int32_t launch_kv_rows(qvx_device* dev, const Layout& L, void* pool, const float* k_rows,
                        const float* v_rows, size_t row_stride_f32, const uint32_t* at_direct,
                        const uint32_t* pos, const uint32_t* blocks, const uint32_t* table_at, size_t n,
-                       int kind, cudaStream_t s);
+                       size_t pool_blocks, int kind, cudaStream_t s);
 int32_t launch_attn_prelude(qvx_device* dev, const Layout& L, size_t heads, size_t s, float* q, float* k_new, float* v_new,
                             const qvx_prelude* p, cudaStream_t stream);
 int32_t launch_block_copy(qvx_device* dev, const Layout& L, void* pool, const uint32_t* src,
-                          const uint32_t* dst, size_t n, cudaStream_t s);
+                          const uint32_t* dst, size_t n, size_t pool_blocks, cudaStream_t s);
 
 }  // namespace qvx
 

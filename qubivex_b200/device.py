@@ -88,23 +88,25 @@ class DeviceBuffer:
     handle: int
 
     def __len__(self) -> int:
-        return _lib.load().qvx_buffer_len(self.handle)
+        return self.device.lib.qvx_buffer_len(self.handle)
 
     @property
     def ptr(self) -> int:
-        return _lib.load().qvx_buffer_ptr(self.handle) or 0
+        return self.device.lib.qvx_buffer_ptr(self.handle) or 0
 
     def free(self) -> None:
         if self.handle:
-            _lib.load().qvx_free(self.handle)
+            self.device.lib.qvx_free(self.handle)
             self.handle = 0
 
 
 class CudaDevice:
     """`impl DiscreteDevice for CudaDevice`, the decode-attention subset."""
 
-    def __init__(self, device: int = 0, capacity: int = 0, kv_pool: int = 0, timing: int | bool = False):
-        self.lib = _lib.load()
+    def __init__(self, device: int = 0, capacity: int = 0, kv_pool: int = 0, timing: int | bool = False,
+                 experiments: bool = False):
+        # experiments: the build whose chunk and run-length rules can be set through the environment
+        self.lib = _lib.load(experiments)
         self.h = C.c_void_p()
         cfg = Config(device, capacity, kv_pool, int(timing))  # timing = n: CUDA events around every n-th launch
         rc = self.lib.qvx_open(C.byref(cfg), C.byref(self.h))

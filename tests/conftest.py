@@ -36,3 +36,12 @@ def dev():
     d = CudaDevice(0, timing=True)
     yield d
     d.close()
+
+
+@pytest.fixture(scope="session")
+def dev_x():
+    """A device of the experiment build of the library: the chunk and run-length rules follow the environment."""
+    from qubivex_b200.device import CudaDevice
+    d = CudaDevice(0, timing=True, experiments=True)
+    yield d
+    d.close()

@@ -393,17 +393,17 @@ def test_batch_invariance_when_ctas_stream_many_ragged_items(dev):
 
 @pytest.mark.parametrize("dtype,heads,kvh,d,B", [("bf16", 32, 4, 128, 16), ("f16", 8, 2, 64, 32), ("bf16", 8, 1, 256, 16),
                                                 ("bf16", 24, 2, 128, 64)])
-def test_runs_of_chunks_do_not_change_a_single_bit(dev, monkeypatch, dtype, heads, kvh, d, B):
+def test_runs_of_chunks_do_not_change_a_single_bit(dev, dev_x, monkeypatch, dtype, heads, kvh, d, B):
     # Work items are runs of consecutive chunks of a sequence; how long the runs are is the
     # scheduler's choice per op.  Every chunk keeps its own state, so the outputs must not move.
     lengths = [3000, 513, 2048, 1, 1537, 4096, 700, 2049] * 3
     c = Case(heads, kvh, d, B, dtype, lengths, seed=95, amp_qk=0.4)
     outs = {}
     for run in ("1", "2", "3", "4"):
-        monkeypatch.setenv("QVX_RUN_CHUNKS", run)
-        outs[run] = c.run_device(dev, variant=qd.ATTN_SPLIT)[1]
+        monkeypatch.setenv("QVX_RUN_CHUNKS", run)   # read by the experiment build only
+        outs[run] = c.run_device(dev_x, variant=qd.ATTN_SPLIT)[1]
     monkeypatch.delenv("QVX_RUN_CHUNKS")
-    outs["auto"] = c.run_device(dev, variant=qd.ATTN_SPLIT)[1]
+    outs["auto"] = c.run_device(dev, variant=qd.ATTN_SPLIT)[1]  # the shipped library, its own choice of runs
     for k, v in outs.items():
         assert np.array_equal(v.view(np.uint32), outs["1"].view(np.uint32)), k
     _, want = c.run_oracle()
@@ -411,7 +411,7 @@ def test_runs_of_chunks_do_not_change_a_single_bit(dev, monkeypatch, dtype, head
     assert ok, err
 
 
-def test_a_step_appended_inside_a_run_lands_in_the_pool(dev, monkeypatch):
+def test_a_step_appended_inside_a_run_lands_in_the_pool(dev_x, monkeypatch):
     # The fused append stores the step's new row from the item that ends the sequence; with runs that
     # item holds several chunks.  Pool bytes and outputs against the oracle, runs of 1 and of 4.
     import ctypes as C
@@ -421,7 +421,7 @@ def test_a_step_appended_inside_a_run_lands_in_the_pool(dev, monkeypatch):
     want_pool, want = c.run_oracle()
     for run in ("1", "4"):
         monkeypatch.setenv("QVX_RUN_CHUNKS", run)
-        got_pool, got = c.run_device(dev, variant=qd.ATTN_SPLIT)   # the host op: sync, then append + attention in one launch
+        got_pool, got = c.run_device(dev_x, variant=qd.ATTN_SPLIT)   # the host op: sync, then append + attention in one launch
         assert np.array_equal(got_pool, want_pool), run
         ok, err = within(got, want, "bf16")
         assert ok, (run, err)

@@ -4,8 +4,10 @@ Some hosts of this backend hand the whole device to the KV pool up front and acc
 byte of it; they cannot let the library malloc scratch in the middle of a decode step.  This
 entry point keeps its scratch in a fixed array inside the library instead.  The test calls it
 through the C ABI twice in a row on different inputs (the second call finds the array as the
-first left it) and checks both results against the ordinary entry point, qvx_attn_decode, on
-the same pool — within the tolerance the other attention tests use.
+first left it) and checks both results twice: against the CPU oracle on the same pool bytes,
+within the tolerance the other attention tests use, and against the ordinary entry point,
+qvx_attn_decode, much more tightly (the two kernels share their arithmetic and their chunks
+and differ only in the order the chunks' results are merged in).
 
 The file sorts last on purpose: a run that stops at the first failure has then run every other
 test.  It builds its own device and pool, so it passes alone in a fresh process as well.
@@ -15,6 +17,8 @@ import ctypes as C
 import numpy as np
 import pytest
 
+import oracle
+from helpers import within
 from qubivex_b200 import device as qd
 from qubivex_b200.device import ptr
 
@@ -61,14 +65,23 @@ def _case(dev, torch, seed, lengths, heads=32, kvh=4, d=128, B=16, dtype=qd.BF16
         assert torch.cuda.mem_get_info()[0] >= free_before
     dev.kernel_times()  # reads the device status word: raises if the kernel refused anything
     dev.lib.qvx_tables_free(tabs)
-    return got.cpu().numpy(), want.cpu().numpy()
+    # the CPU oracle on the same pool bytes
+    geo_o = oracle.geometry(B, kvh, d, dtype, oracle.LAYOUT_NATIVE)
+    rc, ref = oracle.attn_decode(pool.view(torch.uint8).cpu().numpy(), geo_o, heads, q.cpu().numpy(), pos, blocks, table_at, threads=8)
+    assert rc == 0
+    return got.cpu().numpy(), want.cpu().numpy(), ref, "bf16" if dtype == qd.BF16 else "f16"
 
 
-def _close(got, want):
-    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+def _close(case):
+    got, want, ref, dtype = case
     assert np.all(np.isfinite(got))
-    assert np.all(err <= 2e-3 + 1e-2 * np.abs(want)), float(err.max())
-    return float(err.max())
+    ok, err = within(got, ref, dtype)           # the parity bar, against the oracle
+    assert ok, err
+    ok, err = within(want, ref, dtype)
+    assert ok, err
+    # against the ordinary entry point: same chunks, same arithmetic, another merge order
+    diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert np.all(diff <= 2e-5 + 1e-4 * np.abs(want)), float(diff.max())
 
 
 def test_two_calls_in_a_row_match_the_ordinary_entry_point():
@@ -76,13 +89,11 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
     dev = qd.CudaDevice(0)
     try:
         # first call: sequences of one chunk and of several, a ragged tail, a single position
-        got, want = _case(dev, torch, 1, [1, 17, 511, 512, 513, 1300, 4096], first_launch=True)
-        _close(got, want)
+        _close(_case(dev, torch, 1, [1, 17, 511, 512, 513, 1300, 4096], first_launch=True))
         # second call at once, other shapes: it finds the array as the first call left it
-        got, want = _case(dev, torch, 2, [2048, 700, 33, 3000], heads=16, kvh=4, d=64, B=32, dtype=qd.F16, first_launch=True)
-        _close(got, want)
-        got, want = _case(dev, torch, 3, [900, 1025], heads=8, kvh=2)
-        _close(got, want)
+        _close(_case(dev, torch, 2, [2048, 700, 33, 3000], heads=16, kvh=4, d=64, B=32, dtype=qd.F16, first_launch=True))
+        _close(_case(dev, torch, 3, [900, 1025], heads=8, kvh=2))                 # groups of 4 query heads
+        _close(_case(dev, torch, 4, [1500, 64, 513], heads=24, kvh=2))            # groups of 12: two head groups per KV head
     finally:
         dev.close()
 
@@ -105,3 +116,57 @@ def test_an_op_beyond_the_fixed_array_is_refused_with_its_sizes():
         assert dev.lib.qvx_attn_decode_static(dev.h, C.byref(f32), ptr(x), 8, 1, ptr(x), ptr(x), ptr(x), ptr(x), 0, ptr(x), None) == -2
     finally:
         dev.close()
+
+
+def test_a_position_beyond_the_callers_bound_is_refused_and_reported_once():
+    """max_pos is the host's promise about pos[]; the scratch was sized by it.  A sequence that breaks it
+    is left alone (the kernel returns before it touches memory), the device's status word says so, the
+    host reports it at its next wait on the device — once — and the device is usable afterwards."""
+    torch = pytest.importorskip("torch")
+    dev = qd.CudaDevice(0)
+    try:
+        heads, kvh, d, B = 8, 2, 128, 16
+        geo = qd.geometry(B, kvh, d, qd.BF16, qd.LAYOUT_NATIVE)
+        bb = qd.block_bytes(geo)
+        lengths = np.array([300, 1301], dtype=np.int64)          # the second breaks the bound below
+        nb = (lengths + B - 1) // B
+        pool = torch.randn(int(nb.sum()) * bb // 2, device="cuda").to(torch.bfloat16)
+        q = torch.randn((2, heads, d), device="cuda")
+        d_pos = torch.from_numpy((lengths - 1).astype(np.int32)).cuda()
+        d_blocks = torch.arange(int(nb.sum()), dtype=torch.int32, device="cuda")
+        d_table_at = torch.tensor([0, int(nb[0])], dtype=torch.int32, device="cuda")
+        out = torch.full_like(q, 7.0)
+        call = lambda max_pos: dev.lib.qvx_attn_decode_static(dev.h, C.byref(geo), ptr(pool), heads, 2, ptr(q), ptr(d_pos), ptr(d_blocks),
+                                                              ptr(d_table_at), max_pos, ptr(out), None)
+        assert call(511) == 0                                   # the launch itself is fine
+        torch.cuda.synchronize()
+        assert torch.all(out[1] == 7.0)                         # nothing written for the sequence past the bound
+        assert not torch.any(out[0] == 7.0)                     # the one inside it was served
+        with pytest.raises(qd.DeviceError, match="beyond the bound"):
+            dev.kernel_times()
+        dev.kernel_times()                                      # reported once: the word is clear again
+        assert call(1300) == 0
+        torch.cuda.synchronize()
+        dev.kernel_times()
+        assert not torch.any(out == 7.0)
+    finally:
+        dev.close()
+
+
+def test_one_thread_may_drive_two_devices():
+    """The kernels' shared-memory opt-in belongs to a device: a thread that opens two must get it on both."""
+    torch = pytest.importorskip("torch")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one GPU here")
+    from helpers import Case
+    for ordinal in (0, 1):
+        dev = qd.CudaDevice(ordinal)
+        try:
+            with torch.cuda.device(ordinal):
+                _close(_case(dev, torch, 5 + ordinal, [700, 1025], heads=8, kvh=2))
+            c = Case(8, 2, 64, 16, "f32", [600, 40, 1100], seed=7)   # the f32 split kernel's opt-in as well
+            _, want = c.run_oracle()
+            _, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
+            assert within(got, want, "f32")[0]
+        finally:
+            dev.close()
