@@ -209,6 +209,7 @@ def parity_sample(dev, pool, geo, shape, lengths, blocks, table_at, q_dev, out_d
     err = np.abs(got.astype(np.float64) - want[0].astype(np.float64))
     ok = rc == 0 and bool(np.all(err <= 2e-3 + 1e-2 * np.abs(want[0])))
     return {"sequence": int(seq), "layer": "last", "positions": n, "max_abs_err": float(err.max()),
+            "max_abs_oracle": float(np.abs(want[0]).max()), "max_err_over_allowed": float((err / (2e-3 + 1e-2 * np.abs(want[0]))).max()),
             "tolerance": "2e-3 + 1e-2 * |oracle|", "ok": ok}
 
 
@@ -313,7 +314,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         step(t)
     p1.record()
     barrier()
-    repeats = torch.tensor([max(1, int(np.ceil(args.min_seconds * 1e3 / max(p0.elapsed_time(p1), 1e-3))))], device="cuda")
+    pilot_ms = p0.elapsed_time(p1)
+    repeats = torch.tensor([max(1, int(np.ceil(args.min_seconds * 1e3 / max(pilot_ms, 1e-3))))], device="cuda")
     if dist is not None:
         dist.all_reduce(repeats, op=dist.ReduceOp.MAX)
     R = int(repeats.item())
@@ -412,6 +414,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                      "traffic": algo * DRAM_TRAFFIC_PER_ALGORITHMIC_BYTE, "algorithmic_bytes_per_launch": algo,
                      "launch_us": launch_us, "launches": int(launches),
                      "launch_alone_us": attn_ns / max(attn_launches, 1) / 1e3, "launches_timed_alone": int(attn_launches),
+                     "burst": {"launch_us": pilot_ms * 1e3 / (K * layers), "frac": algo / (pilot_ms * 1e-3 / (K * layers)) / 1e9 / peak,
+                               "frac_of_8000": algo / (pilot_ms * 1e-3 / (K * layers)) / 1e9 / 8000.0,
+                               "what": "the first block of K steps after the warm-up (this rank), tens of milliseconds: the device has "
+                                       "not reached its power cap yet; the figures above are the sustained ones"},
                      "kernels_us_per_launch": {k: (v[1] / v[0] / 1e3 if v[0] else 0.0) for k, v in kt.items() if v[0]}},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "call": "qvx_paged_attention_host x layers per step: synchronous, one op per layer, as DiscreteDevice::routed_moe",

@@ -265,9 +265,13 @@ int32_t qvx_paged_attention_host(qvx_device *dev, qvx_buffer *pool, const qvx_ge
                                  size_t n_sync, float *out_host, uint32_t variant);
 
 /* The same op with the waits taken out: the copies and kernels are queued on the device's
- * own stream from pinned staging memory and `qvx_wait` (or the next synchronous call)
- * completes them, so several layers' ops overlap their copies with each other's kernels.
- * The host arrays must stay unchanged until then; out_host is written by then. */
+ * streams and `qvx_wait` (or the next synchronous call) completes them, so several layers' ops
+ * overlap their copies with each other's kernels.  q, k_new, v_new, sync and out are copied
+ * straight from / to the caller's arrays (only the block tables and the work list built from
+ * them pass through the library's pinned staging ring): give PINNED host memory
+ * (cudaHostAlloc / cudaHostRegister) for the copies to be asynchronous; from pageable memory
+ * the CUDA runtime stages each copy and the call blocks for as long, which serialises the ops.
+ * The host arrays must stay unchanged until the wait; out_host is written by then. */
 int32_t qvx_paged_attention_host_async(qvx_device *dev, qvx_buffer *pool, const qvx_geometry *geo,
                                        size_t heads, size_t s, const float *q_host,
                                        const float *k_new_host, const float *v_new_host,

@@ -155,15 +155,17 @@ def declared_symbols() -> list[str]:
     return sorted(set(re.findall(r"\b(qvx_[a-z0-9_]+)\s*\(", text)) - {"qvx_release_fn"})
 
 
-_libs: dict[bool, C.CDLL] = {}
+_libs: dict = {}
 
 
-def load(experiments: bool = False) -> C.CDLL:
-    """The library (or its experiment build), built first if absent.  Raises when it cannot be loaded."""
+def load(experiments: bool | str = False) -> C.CDLL:
+    """The library (or its experiment build; "short_waits": the test build with short bounded waits), built
+    first if absent.  Raises when it cannot be loaded."""
     if experiments not in _libs:
-        path = _build.LIB_EXPERIMENTS if experiments else _build.LIB
+        short = experiments == "short_waits"
+        path = _build.LIB_SHORT_WAITS if short else _build.LIB_EXPERIMENTS if experiments else _build.LIB
         if not path.exists():
-            _build.build(experiments=experiments)
+            _build.build(experiments=bool(experiments) and not short, short_waits=short)
         lib = C.CDLL(str(path))
         for name, (res, args) in PROTOTYPES.items():
             fn = getattr(lib, name)  # AttributeError here = the build is stale or broken

@@ -22,6 +22,9 @@ CSRC = PKG / "csrc"
 # show which of those move no bit, and the profiling drivers, load it).
 LIB = PKG / "lib" / "libqvx_cuda.so"
 LIB_EXPERIMENTS = PKG / "lib" / "libqvx_cuda_experiments.so"
+# A test build: bounded waits of a few thousand polls and a hook that loses one publication, so that a
+# test can watch a wait run out and the device recover (tests/test_gpu_guards.py).
+LIB_SHORT_WAITS = PKG / "lib" / "libqvx_cuda_shortwaits.so"
 # QVX_LIB / QVX_NVCC_EXTRA build one more variant (kernel experiments) and make it the library loaded.
 if os.environ.get("QVX_LIB"):
     LIB = Path(os.environ["QVX_LIB"]).resolve()
@@ -57,10 +60,11 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, experiments: bool = False) -> Path:
-    """Compiles what is stale and links the library; `experiments` builds libqvx_cuda_experiments.so."""
-    lib = LIB_EXPERIMENTS if experiments else LIB
-    extra_flags = ["-DQVX_EXPERIMENTS"] if experiments else EXTRA
+def build(force: bool = False, verbose: bool = False, experiments: bool = False, short_waits: bool = False) -> Path:
+    """Compiles what is stale and links the library; `experiments` builds libqvx_cuda_experiments.so,
+    `short_waits` libqvx_cuda_shortwaits.so."""
+    lib = LIB_SHORT_WAITS if short_waits else LIB_EXPERIMENTS if experiments else LIB
+    extra_flags = (["-DQVX_TEST_HOOKS", "-DQVX_WAIT_LIMIT=4096"] if short_waits else ["-DQVX_EXPERIMENTS"] if experiments else EXTRA)
     obj_dir = ROOT / "build" / ("obj-" + lib.stem)
     obj_dir.mkdir(parents=True, exist_ok=True)
     lib.parent.mkdir(parents=True, exist_ok=True)
@@ -98,5 +102,5 @@ def build(force: bool = False, verbose: bool = False, experiments: bool = False)
 
 
 if __name__ == "__main__":
-    for x in (False, True):
-        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, experiments=x))
+    for kw in ({}, {"experiments": True}, {"short_waits": True}):
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, **kw))

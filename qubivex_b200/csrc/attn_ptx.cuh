@@ -10,7 +10,12 @@ namespace qvx {
 
 constexpr int TILE = 16;              // positions per tile
 constexpr uint32_t NO_PART = 0xffffffffu;
-constexpr uint32_t WAIT_LIMIT = 1u << 20;
+// Polls a bounded wait makes before it gives up (with the back-off below: around a second).  A test build
+// makes it small so that a wait can be seen to run out.
+#ifndef QVX_WAIT_LIMIT
+#define QVX_WAIT_LIMIT (1u << 20)
+#endif
+constexpr uint32_t WAIT_LIMIT = QVX_WAIT_LIMIT;
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -100,6 +100,7 @@ struct StreamArgs {
     uint32_t page_bytes, tiles_per_block, heads, item_words, n_items, kv_out;
     uint32_t overlap;       // the pool and the tables do not depend on the work before this launch in the stream
     uint32_t trace_id;      // the launch's number (experiment builds that trace; otherwise unused)
+    uint32_t test_hooks;    // test builds (-DQVX_TEST_HOOKS): 1 = lose one publication; otherwise unused
     float scale_log2;
 };
 
@@ -361,26 +362,27 @@ __device__ __forceinline__ bool wait_published(const uint32_t* published, uint32
 // node's last arrival for certain, and the entries before it can be folded now: when the item's
 // own result is ready only that (and the entries after it, if any) remain.  Returns whether
 // `r` holds that prefix.
+enum : uint32_t { FOLD_NOT_YET = 0, FOLD_DONE = 1, FOLD_GAVE_UP = 2 };
 template <int D>
-__device__ __forceinline__ bool fold_ahead(const StreamArgs& a, const Mail& it, uint32_t lane, Running<D>& r) {
+__device__ __forceinline__ uint32_t fold_ahead(const StreamArgs& a, const Mail& it, uint32_t lane, Running<D>& r) {
     constexpr uint32_t PART_STRIDE = 8 * D + 16;
     const MergeNode mn = merge_node_of(it.chunk, it.nch);
     const uint32_t node = mn.node, first = mn.first, size = mn.size, mine = it.chunk - first;
-    if (size < 2) return false;
+    if (size < 2) return FOLD_GAVE_UP;  // nothing to fold, now or later
     const uint32_t* claimed = a.counters + it.counter + 2 * node;
     // Both words in one round trip: lane 0 reads `claimed`, lane 1 `published`.
     uint32_t word = 0;
     if (lane < 2) word = *reinterpret_cast<const volatile uint32_t*>(claimed + lane);
-    if (__shfl_sync(0xffffffffu, word, 0) != size - 1) return false;
+    if (__shfl_sync(0xffffffffu, word, 0) != size - 1) return FOLD_NOT_YET;
     if (__shfl_sync(0xffffffffu, word, 1) != size - 1 && !wait_published(claimed + 1, size - 1))
-        return false;  // the caller's own wait reports a failure
+        return FOLD_GAVE_UP;  // a bounded wait ran out: no second try; the arrival's own wait reports it
     fence_acq_rel_gpu();
     r.clear();
     float4 none[8 * D / 4 / 32];
 #pragma unroll
     for (int j = 0; j < 8 * D / 4 / 32; j++) none[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     fold_range<D, (8 * D / 4 / 32 <= 8 ? 3 : 1)>(r, a.partials + (size_t)(it.part0 + first) * PART_STRIDE, 0, mine, NO_PART, none, 0.f, lane);
-    return true;
+    return FOLD_DONE;
 }
 
 // Run by the epilogue warp with a chunk's merged result in registers (E, Eml as in fold_range).
@@ -414,9 +416,10 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
         uint32_t* published = claimed + 1;
         float* p0 = a.partials + (size_t)(part_base + first) * PART_STRIDE;
         if (!ahead) {
-            uint32_t last = 0;
-            if (lane == 0) last = atomicAdd(claimed, 1u) == size - 1 ? 1u : 0u;
-            last = __shfl_sync(0xffffffffu, last, 0);
+            uint32_t ticket = 0;
+            if (lane == 0) ticket = atomicAdd(claimed, 1u);
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            const bool last = ticket == size - 1;
             tr.mark(last ? 14 : 17);  // claim answered
             if (!last) {
                 float* pe = p0 + (size_t)mine * PART_STRIDE;
@@ -426,6 +429,11 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
                 if (lane < 16) pe[8 * D + lane] = Eml;
                 fence_acq_rel_gpu();
                 __syncwarp();
+#ifdef QVX_TEST_HOOKS
+                // A test build can lose one publication (sequence 0's first group, the first arrival at its node): the node's last
+                // arrival must then give up its bounded wait, report it, and leave the device usable.
+                if (a.test_hooks == 1u && it.seq == 0 && it.head0 == 0 && ticket == 0 && n == it.nch) return;
+#endif
                 if (lane == 0) atomicAdd(published, 1u);
                 return;
             }
@@ -728,16 +736,15 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             m.nch = mailbox[ns].nch; m.counter = mailbox[ns].counter; m.stop = mailbox[ns].stop; m.chunk = mailbox[ns].chunk;
             if (m.stop) return;
             // While they stream it: if the item is its node's last arrival, fold what precedes it.
-            bool ahead = m.chunk != NO_PART && fold_ahead<D>(a, m, lane, run);
-            if (m.chunk != NO_PART && !ahead && merge_node_of(m.chunk, m.nch).size >= 2) {
-                // Not yet: some other chunk of the node has not arrived.  This warp has nothing else to do until the
-                // item's states are ready, so it looks again (a round trip to the L2 each time) in between.
-                for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-                    const uint32_t ready = mbar_try_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1) ? 1u : 0u;
-                    if (__shfl_sync(0xffffffffu, ready, 0)) break;
-                    if ((ahead = fold_ahead<D>(a, m, lane, run))) break;
-                }
+            uint32_t folded = m.chunk != NO_PART ? fold_ahead<D>(a, m, lane, run) : (uint32_t)FOLD_GAVE_UP;
+            // Not yet: some other chunk of the node has not arrived.  This warp has nothing else to do until the
+            // item's states are ready, so it looks again (a round trip to the L2 each time) in between.
+            for (uint32_t i = 0; folded == FOLD_NOT_YET && i < WAIT_LIMIT; i++) {
+                const uint32_t ready = mbar_try_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1) ? 1u : 0u;
+                if (__shfl_sync(0xffffffffu, ready, 0)) break;
+                folded = fold_ahead<D>(a, m, lane, run);
             }
+            const bool ahead = folded == FOLD_DONE;
             tr.mark(ahead ? 18 : 19);  // note read (and the node's other entries folded)
             if (!__all_sync(0xffffffffu, mbar_wait(rfull0 + ms * 8, (kp / MAIL_SLOTS) & 1))) return;
             tr.mark(10);  // states ready
@@ -1074,6 +1081,10 @@ int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, con
     a.heads = (uint32_t)t->heads; a.item_words = t->item_words; a.n_items = (uint32_t)t->n_items;
     a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;
     a.trace_id = 0;
+    a.test_hooks = 0;
+#ifdef QVX_TEST_HOOKS
+    if (const char* v = getenv("QVX_TEST_LOSE_A_PUBLICATION")) a.test_hooks = atol(v) ? 1u : 0u;
+#endif
     // bf16 carries 8 mantissa bits: the queries and the probabilities go through the tensor cores as a value and
     // a remainder (bit 0: queries, bit 1: probabilities).  An experiment build can leave passes out
     // (QVX_ATTN_ONE_PASS = 1: both, 2: the probabilities', 3: the queries').

@@ -195,13 +195,14 @@ static int32_t resize_staging(qvx_device* dev, size_t cap) {
     return QVX_OK;
 }
 
-static int32_t wait_locked(qvx_device* dev) {
+// `own_stream_only`: everything in flight was queued on the device's own stream (a serial op).
+static int32_t wait_locked(qvx_device* dev, bool own_stream_only = false) {
     uint64_t t0 = now_ns();
     DeviceExtras* x = extras(dev);
-    cudaError_t e = cudaStreamSynchronize(x->h2d);
+    cudaError_t e = own_stream_only ? cudaSuccess : cudaStreamSynchronize(x->h2d);
     if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(x->kernels2);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(x->d2h);
+    if (e == cudaSuccess && !own_stream_only) e = cudaStreamSynchronize(x->kernels2);
+    if (e == cudaSuccess && !own_stream_only) e = cudaStreamSynchronize(x->d2h);
     x->last_kernels[0] = x->last_kernels[1] = nullptr;
     dev->xfer.wait_ns += now_ns() - t0;
     dev->xfer.fence_waits++;
@@ -946,7 +947,10 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
                                       const uint32_t* pos, const uint32_t* blocks, size_t n_blocks,
                                       const uint32_t* table_at, const float* sync, const uint32_t* sync_to,
                                       size_t n_sync, float* out, uint32_t variant, const qvx_prelude* pre = nullptr,
-                                      float* k_back = nullptr, float* v_back = nullptr) {
+                                      float* k_back = nullptr, float* v_back = nullptr, bool serial = false) {
+    // `serial`: the caller waits for this op right away and nothing else is in flight, so copies in, kernels and
+    // copies out all go on the device's own stream in order: no event hand-over between streams (each costs
+    // microseconds of latency that nothing would hide).
     uint64_t t0 = now_ns();
     if (pre && !prelude_ok(pre))
         return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: a prelude needs a RoPE table, a clip >= 0 and both norms or neither");
@@ -998,31 +1002,16 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     op.begin = base; op.end = base + total;
     op.in_done = take_event(x); op.kernels_done = take_event(x); op.out_done = take_event(x);
 
-    fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at, ctas, cache, split);
-    // A position listed twice: the later row wins (the reference writes them in list order).
-    uint32_t* st = (uint32_t*)(hs + o_syncto);
-    {
-        std::unordered_set<uint32_t> seen;
-        seen.reserve(n_sync * 2);
-        for (size_t i = n_sync; i-- > 0;) st[i] = seen.insert(sync_to[i]).second ? sync_to[i] : 0xffffffffu;
-    }
-    qvx_tables* t = new qvx_tables;
-    t->dev = dev; t->L = L; t->pool_blocks = held; t->heads = heads; t->s = s; t->n_blocks = n_blocks;
-    bind_image(t, im, ds + o_img);
-    t->owns_dmem = false;
-    op.tables = t;
-    cudaEventRecord(op.out_done, x->d2h);  // re-recorded after the copy out; a failed op's slice is free at once
-    if (split) {
-        rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
-        if (rc) return rc;
-    }
-
+    serial = serial && x->ops.size() == 1;  // (this op is the only one in the list)
     // The scratch half the attention launch will take decides the stream: every user of a half is on
     // the same stream, so two launches never share a half at the same time.
-    const uint32_t lane = split ? (dev->scratch_half & 1u) : 0u;
-    cudaStream_t h2d = x->h2d, cs = lane ? x->kernels2 : dev->stream, d2h = x->d2h;
-    if (!independent && x->last_kernels[lane ^ 1u]) cudaStreamWaitEvent(cs, x->last_kernels[lane ^ 1u], 0);
-    cudaError_t e = cudaMemcpyAsync(ds + o_img, hs + o_img, im.bytes + up(4 * n_sync), cudaMemcpyHostToDevice, h2d);
+    const uint32_t lane = split && !serial ? (dev->scratch_half & 1u) : 0u;
+    cudaStream_t h2d = serial ? dev->stream : x->h2d, cs = lane ? x->kernels2 : dev->stream, d2h = serial ? dev->stream : x->d2h;
+    if (!serial) cudaEventRecord(op.out_done, x->d2h);  // re-recorded after the copy out; a failed op's slice is free at once
+    // The caller's arrays go first, straight from where they are (pinned memory makes these true asynchronous
+    // copies; from pageable memory the runtime stages them and the call blocks for as long): they are on their
+    // way while the work list is built below.
+    cudaError_t e = cudaSuccess;
     size_t in_bytes = im.bytes + 4 * n_sync;
     auto copy_in = [&](size_t off, const void* src, size_t bytes) {
         if (e == cudaSuccess && bytes) e = cudaMemcpyAsync(ds + off, src, bytes, cudaMemcpyHostToDevice, h2d);
@@ -1036,9 +1025,31 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
         copy_in(o_rope, pre->rope, 4 * s * L.d);
         if (norms) { copy_in(o_qn, pre->q_norm, 4 * q_out); copy_in(o_kn, pre->k_norm, 4 * kv_out); }
     }
+
+    fill_image(im, hs + o_img, L, heads, s, pos, blocks, n_blocks, table_at, ctas, cache, split);
+    // A position listed twice: the later row wins (the reference writes them in list order).
+    uint32_t* st = (uint32_t*)(hs + o_syncto);
+    {
+        std::unordered_set<uint32_t> seen;
+        seen.reserve(n_sync * 2);
+        for (size_t i = n_sync; i-- > 0;) st[i] = seen.insert(sync_to[i]).second ? sync_to[i] : 0xffffffffu;
+    }
+    qvx_tables* t = new qvx_tables;
+    t->dev = dev; t->L = L; t->pool_blocks = held; t->heads = heads; t->s = s; t->n_blocks = n_blocks;
+    bind_image(t, im, ds + o_img);
+    t->owns_dmem = false;
+    op.tables = t;
+    if (split) {
+        rc = ensure_partials(dev, attn_partial_floats(t), t->n_counters);
+        if (rc) return rc;
+    }
+    if (!serial && !independent && x->last_kernels[lane ^ 1u]) cudaStreamWaitEvent(cs, x->last_kernels[lane ^ 1u], 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ds + o_img, hs + o_img, im.bytes + up(4 * n_sync), cudaMemcpyHostToDevice, h2d);
     if (e != cudaSuccess) return check_cuda(dev, e, "copy in");
-    cudaEventRecord(op.in_done, h2d);
-    cudaStreamWaitEvent(cs, op.in_done, 0);
+    if (!serial) {
+        cudaEventRecord(op.in_done, h2d);
+        cudaStreamWaitEvent(cs, op.in_done, 0);
+    }
 
     if (pre && s) {  // clip, norms, RoPE on the staged projections: sim.rs:333-357
         qvx_prelude dp = *pre;
@@ -1056,9 +1067,11 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
         rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), (float*)(ds + o_out), variant, cs,
                            (const float*)(ds + o_k), (const float*)(ds + o_v));
     if (rc) return rc;
-    cudaEventRecord(op.kernels_done, cs);
-    x->last_kernels[lane] = op.kernels_done;
-    cudaStreamWaitEvent(d2h, op.kernels_done, 0);
+    if (!serial) {
+        cudaEventRecord(op.kernels_done, cs);
+        x->last_kernels[lane] = op.kernels_done;
+        cudaStreamWaitEvent(d2h, op.kernels_done, 0);
+    }
     if (s) {
         e = cudaMemcpyAsync(out, ds + o_out, 4 * s * q_out, cudaMemcpyDeviceToHost, d2h);
         if (e == cudaSuccess && k_back) e = cudaMemcpyAsync(k_back, ds + o_k, 4 * s * kv_out, cudaMemcpyDeviceToHost, d2h);
@@ -1100,9 +1113,10 @@ int32_t qvx_paged_attention_host(qvx_device* dev, qvx_buffer* pool, const qvx_ge
     if (!dev) return QVX_ERR_SHAPE;
     std::lock_guard<std::mutex> lk(dev->mu);
     cudaSetDevice(dev->ordinal);
+    const bool alone = extras(dev)->ops.empty();
     int32_t rc = paged_attention_submit(dev, pool, geo, heads, s, q, k_new, v_new, pos, blocks, n_blocks, table_at,
-                                        sync, sync_to, n_sync, out, variant);
-    int32_t rc2 = wait_locked(dev);
+                                        sync, sync_to, n_sync, out, variant, nullptr, nullptr, nullptr, alone);
+    int32_t rc2 = wait_locked(dev, alone);
     return rc ? rc : rc2;
 }
 
@@ -1114,9 +1128,10 @@ int32_t qvx_attention_stage_host(qvx_device* dev, qvx_buffer* pool, const qvx_ge
     std::lock_guard<std::mutex> lk(dev->mu);
     cudaSetDevice(dev->ordinal);
     if (!prelude) return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: no prelude given");
+    const bool alone = extras(dev)->ops.empty();
     int32_t rc = paged_attention_submit(dev, pool, geo, heads, s, q, k_new, v_new, pos, blocks, n_blocks, table_at, sync,
-                                        sync_to, n_sync, out, variant, prelude, k_new, v_new);
-    int32_t rc2 = wait_locked(dev);
+                                        sync_to, n_sync, out, variant, prelude, k_new, v_new, alone);
+    int32_t rc2 = wait_locked(dev, alone);
     return rc ? rc : rc2;
 }
 

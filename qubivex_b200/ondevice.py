@@ -12,7 +12,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from .device import ATTN_AUTO, CudaDevice, DeviceBuffer, OutOfDeviceMemory, block_bytes
-from .kvpool import KvPool, Mirror, blocks_for
+from .kvpool import KvPool, Mirror, PrefixCache, blocks_for
 
 
 @dataclass
@@ -23,6 +23,20 @@ class AttnSeq:
     host_v: np.ndarray
     pos: int
     epoch: int = 0
+
+
+@dataclass
+class Retained:
+    """What the prefix index keeps of a finished conversation.  The reference's value is the whole host cache
+    (`PrefixCache<KvCache>`, crates/qubivex-runtime/src/engine.rs:1684-1699) and a hit copies it; its stated plan
+    for paged KV is that the value "would be a set of pages, and a hit would share pages copy-on-write instead
+    of copying them" (docs/decisions/ADR-016-KV-SUBSYSTEM.md:82-89).  This is that value: the sequence's blocks in
+    the pool (a `Mirror`, reference-counted) and the host cache's rows, which stay the authority the pool can be
+    resynced from."""
+    mirror: Mirror
+    host_k: np.ndarray   # [kv_head][position][head_dim]
+    host_v: np.ndarray
+    tokens: int          # positions the entry covers
 
 
 class OnDevice:
@@ -36,8 +50,13 @@ class OnDevice:
         self._buffer: DeviceBuffer | None = None
         self._refused = False
         self.routed = 0
+        self.retained: PrefixCache | None = None
 
     def close(self) -> None:
+        if self.retained is not None:
+            self.retained.clear()      # every retained sequence gives its blocks back
+            self.retained.delete()
+            self.retained = None
         if self._buffer is not None:
             self._buffer.free()
             self._buffer = None
@@ -100,3 +119,51 @@ class OnDevice:
             return out
         finally:
             self.kv.free_plan(plan)
+
+    # -- prefix reuse over shared blocks (Engine::restore / Engine::retain, engine.rs:1659-1699) --------------
+    def retain_prefixes(self, budget_blocks: int) -> PrefixCache:
+        """Turns prefix reuse on: finished sequences are kept, up to `budget_blocks` blocks of the pool in all
+        (an entry's cost is the blocks it holds; the index evicts the oldest entries beyond the budget,
+        crates/qubivex-kv-cache/src/lib.rs:146-199).  An evicted entry's blocks go back to the free list once
+        the last hit on it has been released -- except those a forked sequence still shares."""
+        self.retained = PrefixCache(budget_blocks, on_release=lambda kept: kept.mirror.drop())
+        return self.retained
+
+    def retain(self, scope: str | None, tokens, mirror: Mirror, host_k: np.ndarray, host_v: np.ndarray) -> bool:
+        """Engine::retain: the finished sequence moves into the index (no copy); the caller lets go of `mirror`.
+        False when the index did not keep it (over budget, or an entry already covers it): its blocks are
+        released at once."""
+        if self.retained is None:
+            mirror.drop()
+            return False
+        layers = 0
+        cost = 0
+        while True:
+            n = len(mirror.blocks(layers))
+            if n == 0:
+                break
+            cost += n
+            layers += 1
+        n_tok = len(tokens)
+        return self.retained.insert(scope, tokens, cost, Retained(mirror, host_k[:, :n_tok].copy(), host_v[:, :n_tok].copy(), n_tok))
+
+    def restore(self, scope: str | None, prompt, host_k: np.ndarray, host_v: np.ndarray, epoch: int = 0):
+        """Engine::restore: the longest retained prefix of `prompt` in `scope`, if any.  Returns
+        (mirror, reuse): a new sequence that SHARES the blocks holding positions 0..reuse of the retained one
+        (a table copy and reference counts: no KV byte moves; the first append into a shared, partly filled
+        block copies that block, see KvPool.attention_plan), and the host cache's first `reuse` rows copied
+        into host_k / host_v (the host cache stays authoritative, as KvCache::restore_from keeps it,
+        crates/qubivex-arch/src/lib.rs:409-432).  (None, 0) on a miss."""
+        if self.retained is None:
+            return None, 0
+        found = self.retained.lookup(scope, prompt)
+        if found is None:
+            return None, 0
+        kept, reuse, hit = found
+        try:
+            mirror = kept.mirror.fork(reuse, epoch)
+            host_k[:, :reuse] = kept.host_k[:, :reuse]
+            host_v[:, :reuse] = kept.host_v[:, :reuse]
+        finally:
+            self.retained.release(hit)   # the fork holds its own references: the entry may be evicted from now on
+        return mirror, reuse

@@ -95,3 +95,26 @@ def test_moves_that_name_a_block_past_the_declared_pool_are_skipped(dev):
     assert bool((rows[5] == 1).all())             # the move inside the pool happened
     assert bool((rows[6] == 0x5A).all())          # a source past the end is not read either
     _expect_out_of_pool(dev)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_recovers(monkeypatch):
+    """Every wait in the attention kernel is bounded.  A test build of the library (bounded waits of 4096 polls,
+    and a hook that loses one chunk's publication) shows what happens when one runs out: the chunk that
+    finishes the sequence waits for an entry that never comes, gives up by itself, the launch ends, the host
+    call reports it, and the next op on the same device is right again."""
+    from helpers import Case, within
+    dev = qd.CudaDevice(0, experiments="short_waits")
+    try:
+        c = Case(8, 2, 128, 16, "bf16", [1300, 600], seed=77, amp_qk=0.4)       # sequence 0: three chunks, one merge node
+        _, want = c.run_oracle()
+        _, got = c.run_device(dev, variant=qd.ATTN_SPLIT)                      # the test build itself computes correctly
+        assert within(got, want, "bf16")[0]
+        monkeypatch.setenv("QVX_TEST_LOSE_A_PUBLICATION", "1")
+        with pytest.raises(qd.DeviceError, match="gave up a bounded wait"):
+            c.run_device(dev, variant=qd.ATTN_SPLIT)
+        monkeypatch.delenv("QVX_TEST_LOSE_A_PUBLICATION")
+        _, again = c.run_device(dev, variant=qd.ATTN_SPLIT)                    # counters and queue were reset with the report
+        assert within(again, want, "bf16")[0]
+        dev.kernel_times()
+    finally:
+        dev.close()

@@ -550,3 +550,73 @@ def test_narrowing_edge_values_have_the_oracles_bytes(dev, dtype):
     finally:
         buf.free()
     assert np.array_equal(got, pool_o)
+
+
+# ---- several request threads on one device --------------------------------------------------------
+def test_four_threads_submit_ops_on_one_device(dev):
+    """crates/qubivex-runtime/tests/discrete.rs:772-801: four request threads share the device.  Each runs its own
+    sequences on its own pool buffer through the synchronous host call, eight ops in a row, and checks every
+    result (pool bytes and outputs) against the oracle."""
+    import threading
+    cases = [Case(32, 4, 128, 16, "bf16", [700 + 37 * i, 1025, 64 + i, 2100], seed=300 + i, amp_qk=0.4) for i in range(4)]
+    wants = [c.run_oracle() for c in cases]
+    errors = []
+
+    def request(i):
+        try:
+            for rep in range(8):
+                got_pool, got = cases[i].run_device(dev, variant=qd.ATTN_SPLIT if rep % 2 else qd.ATTN_AUTO)
+                assert np.array_equal(got_pool, wants[i][0]), (i, rep)
+                ok, err = within(got, wants[i][1], "bf16")
+                assert ok, (i, rep, err)
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=request, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    dev.kernel_times()   # the status word is clean
+
+
+# ---- positive controls: the checks above can tell a wrong result ---------------------------------------
+# The reference lists mutations that must each fail a named test (docs/engineering/VULKAN_EXECUTION_AUDIT.md:2499-2510):
+# "reading every key from the first block fails the block-crossing test only", a changed write order fails the bytes.
+# Here the device runs the true op and the ORACLE is given the mutated inputs: the comparison must then fail,
+# exactly where the mutation bites and nowhere else.
+def test_control_tables_that_send_every_position_to_the_first_block_are_noticed(dev):
+    c = Case(8, 2, 64, 16, "bf16", [9, 16, 40, 300], seed=410)     # two sequences inside one block, two that cross
+    got_pool, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
+    _, want = c.run_oracle()
+    assert within(got, want, "bf16")[0]
+    bad = Case(8, 2, 64, 16, "bf16", [9, 16, 40, 300], seed=410)
+    for t in range(4):                                               # every entry of a table becomes the table's first
+        lo = int(bad.table_at[t])
+        hi = int(bad.table_at[t + 1]) if t + 1 < 4 else len(bad.blocks)
+        bad.blocks[lo:hi] = bad.blocks[lo]
+    for r, at in enumerate(c.sync_to):                               # ... and its rows go where those tables say
+        blk, slot = divmod(int(at), 16)
+        t = int(np.searchsorted(c.table_at, np.where(c.blocks == blk)[0][0], side="right")) - 1
+        bad.sync_to[r] = int(bad.blocks[int(bad.table_at[t])]) * 16 + slot
+    bad_pool, bad_want = bad.run_oracle()
+    for t, crosses in enumerate([False, False, True, True]):
+        ok, _ = within(got[t], bad_want[t], "bf16")
+        assert ok != crosses, t                                      # the sequences inside one block still agree
+    assert not np.array_equal(got_pool, bad_pool)
+
+
+def test_control_duplicate_sync_rows_written_in_the_other_order_are_noticed(dev):
+    c = Case(4, 2, 64, 16, "bf16", [40], seed=3)
+    c.sync_to = np.concatenate([c.sync_to, c.sync_to[5:9]])
+    extra = np.random.default_rng(5).standard_normal((4, c.sync.shape[1]), dtype=np.float32)
+    c.sync = np.concatenate([c.sync, extra])
+    got_pool, got = c.run_device(dev)
+    want_pool, _ = c.run_oracle()
+    assert np.array_equal(got_pool, want_pool)                       # the later duplicate wins on both sides
+    n = len(c.sync_to)
+    c.sync_to, c.sync = c.sync_to[::-1].copy(), c.sync[::-1].copy()  # the oracle writes them in the other order
+    bad_pool, bad_want = c.run_oracle()
+    assert not np.array_equal(got_pool, bad_pool)                    # the earlier duplicate won there: the bytes differ
+    assert not within(got, bad_want, "bf16")[0]

@@ -206,6 +206,133 @@ def test_c3_shared_prefix_and_copy_on_write(dev, prefix, copies):
     od.close()
 
 
+# ---- C3 through the prefix index: lookup -> shared blocks -> copy-on-write -> retain -> eviction ----
+def test_c3_prefix_hits_share_blocks_through_the_index(dev):
+    """The request flow of Engine::restore / Engine::retain (crates/qubivex-runtime/src/engine.rs:1659-1699) with
+    the index's value a set of pages (docs/decisions/ADR-016-KV-SUBSYSTEM.md:82-89): a finished conversation of
+    8192 + 8 tokens is retained; eight requests in its scope find it by lookup and share its 513 blocks; each
+    copies the partly filled block on its first append; another scope does not hit; an entry evicted while a
+    hit on it is held lives until the hit goes; finished sequences are retained in turn and the budget evicts the
+    oldest, whose own blocks return to the free list.  Attention against the oracle at every step, the pool's
+    bytes at the end, free == blocks after everything is dropped."""
+    heads, kvh, d, B, blocks = 16, 2, 128, 16, 1200
+    prefix, sharers_n = 8192 + 8, 8
+    geo_d, geo_o = qd.geometry(B, kvh, d, qd.BF16), oracle.geometry(B, kvh, d, oracle.BF16)
+    rng = np.random.default_rng(1659)
+    scale = d ** -0.5
+    od = OnDevice(dev, geo_d, heads, blocks=blocks)
+    od.kv.set_free_order(rng.permutation(blocks))
+    index = od.retain_prefixes(budget_blocks=1100)
+    n_bytes = blocks * oracle.block_bytes(geo_o)
+    dev.write(od.kv_buffer(), 0, np.zeros(n_bytes, dtype=np.uint8))
+    pool_o = np.zeros(n_bytes, dtype=np.uint8)
+
+    def step(seqs):
+        """decode_step, with the oracle's attention on all host threads (the contexts are 8200 positions)."""
+        s = len(seqs)
+        q = (rng.standard_normal((s, heads, d), dtype=np.float32) * scale).astype(np.float32)
+        k_new = np.stack([sq.host.row(sq.host.len)[0] for sq in seqs])
+        v_new = np.stack([sq.host.row(sq.host.len)[1] for sq in seqs])
+        aseqs = [sq.attn_seq() for sq in seqs]
+        out = od.attention(aseqs, 0, q, k_new, v_new, variant=qd.ATTN_SPLIT)
+        assert out is not None
+        plan = od.last_plan
+        for sq, a in zip(seqs, aseqs):
+            sq.mirror = a.mirror
+        if len(plan.copy_src):
+            assert oracle.block_copy(pool_o, geo_o, plan.copy_src, plan.copy_dst) == 0
+        kv_out = kvh * d
+        sync = np.empty((len(plan.sync_to), 2 * kv_out), dtype=np.float32)
+        for r, (si, p) in enumerate(zip(plan.sync_seq, plan.sync_pos)):
+            sync[r, :kv_out], sync[r, kv_out:] = seqs[int(si)].host.row(int(p))
+        assert oracle.kv_write(pool_o, geo_o, k_new, v_new, plan.pos, plan.blocks, plan.table_at, sync, plan.sync_to) == 0
+        rc, want = oracle.attn_decode(pool_o, geo_o, heads, q, plan.pos, plan.blocks, plan.table_at, threads=8)
+        assert rc == 0
+        for sq in seqs:
+            sq.host.len += 1
+        ok, err = within(out, want, "bf16")
+        assert ok, err
+        return plan
+
+    # a conversation runs 8192 + 8 prompt tokens on the host and one decode step on the device, then ends
+    tokens_a = rng.integers(0, 50000, size=prefix + 1, dtype=np.uint32)
+    owner = Seq(HostCache(kvh, d, prefix + 8, rng, scale))
+    owner.host.len = prefix
+    first = step([owner])
+    assert len(first.sync_to) == prefix and owner.mirror.synced(0) == prefix + 1
+    owner_blocks = owner.mirror.blocks(0).copy()
+    assert len(owner_blocks) == 513
+    assert od.retain("chat-1", tokens_a, owner.mirror, owner.host.k, owner.host.v)
+    assert index.stats().entries == 1 and index.cost() == 513
+    free_after_owner = od.kv.stats().free
+    assert free_after_owner == blocks - 513
+
+    # another scope never sees it; nor does a prompt that shares fewer than MIN_REUSE tokens
+    probe_k, probe_v = np.zeros((kvh, 16, d), np.float32), np.zeros((kvh, 16, d), np.float32)
+    assert od.restore("chat-2", tokens_a, probe_k, probe_v) == (None, 0)
+    short = np.concatenate([tokens_a[:20], rng.integers(50000, 60000, size=30, dtype=np.uint32)])
+    assert od.restore("chat-1", short, probe_k, probe_v) == (None, 0)
+    assert index.stats().hits == 0 and index.stats().lookups == 2
+
+    # eight requests that continue the conversation differently: found through the index, nothing copied
+    sharers = []
+    for i in range(sharers_n):
+        prompt = np.concatenate([tokens_a[:prefix], np.array([60000 + i], dtype=np.uint32)])
+        sq = Seq(HostCache(kvh, d, prefix + 32, rng, scale))
+        sq.mirror, reuse = od.restore("chat-1", prompt, sq.host.k, sq.host.v)
+        assert reuse == prefix                                         # the last prompt token always runs
+        assert np.array_equal(sq.host.k[:, :prefix], owner.host.k[:, :prefix])
+        sq.host.len = prefix
+        sq.tokens = prompt
+        sharers.append(sq)
+    assert index.stats().hits == sharers_n and index.stats().tokens_reused == sharers_n * prefix
+    assert od.kv.stats().free == free_after_owner                     # a hit takes no block
+    assert od.kv.refcount(int(owner_blocks[0])) == 1 + sharers_n and od.kv.refcount(int(owner_blocks[512])) == 1 + sharers_n
+    lone = Seq(HostCache(kvh, d, 400, rng, scale))                    # the other scope's request runs its own prompt
+    lone.host.len = 300
+
+    plan = step(sharers + [lone])
+    assert len(plan.copy_src) == sharers_n and set(plan.copy_src.tolist()) == {int(owner_blocks[512])}   # the partly filled block, once per sharer
+    assert od.kv.stats().cow_copies == sharers_n and len(plan.sync_to) == 300
+    assert od.kv.refcount(int(owner_blocks[512])) == 1                # only the retained entry still holds it
+    for sq in sharers:
+        assert sq.mirror.blocks(0)[:512].tolist() == owner_blocks[:512].tolist()
+    for _ in range(8):                                                # on into a fresh block at position 8208
+        plan = step(sharers + [lone])
+        assert len(plan.copy_src) == 0 and len(plan.sync_to) == 0
+    assert all(len(sq.mirror.blocks(0)) == 514 for sq in sharers)
+
+    # an entry evicted while a hit on it is held lives until the hit is released (lib.rs:330-347)
+    kept, reuse, hit = index.lookup("chat-1", sharers[0].tokens)
+    assert index.evict_oldest() and index.stats().entries == 0
+    late = Seq(HostCache(kvh, d, prefix + 32, rng, scale))
+    late.mirror = kept.mirror.fork(reuse)                             # still usable: the hit keeps the value alive
+    free_before_release = od.kv.stats().free
+    index.release(hit)                                                # now the retained sequence lets go of its blocks
+    assert od.kv.stats().free == free_before_release                  # ... all of which somebody still shares
+    late.mirror.drop()
+    assert od.kv.stats().free == free_before_release + 1              # the owner's partly filled block had one holder left
+    plan = step(sharers + [lone])                                     # the sharers decode on over the evicted entry's blocks
+
+    # finished sequences are retained in turn; the budget (1100 blocks) holds two of 514, the third evicts the oldest
+    done = sharers[:3]
+    for i, sq in enumerate(done):
+        toks = np.concatenate([sq.tokens, rng.integers(0, 50000, size=sq.host.len - len(sq.tokens), dtype=np.uint32)])
+        free_before = od.kv.stats().free
+        assert od.retain("chat-1", toks, sq.mirror, sq.host.k, sq.host.v)
+        if i < 2:
+            assert od.kv.stats().free == free_before
+        else:
+            assert index.stats().evicted == 2 and index.stats().entries == 2
+            assert od.kv.stats().free == free_before + 2              # the evicted sequence's own two blocks (its copy and the one after)
+    assert np.array_equal(read_pool(dev, od, n_bytes), pool_o)
+    for sq in sharers[3:] + [lone]:
+        sq.mirror.drop()
+    index.clear()
+    assert od.kv.stats().free == blocks
+    od.close()
+
+
 # ---- C4: churn, compaction, then attention ---------------------------------------------------------
 def test_c4_churn_compaction_then_attention(dev):
     """32 q / 8 kv heads of 128, bf16, block 32.  Sequences retire and arrive at random; a compaction

@@ -223,3 +223,103 @@ def test_random_traffic_matches_the_restatement():
         m.drop()
     assert pool.stats().free == N
     pool.delete()
+
+
+# ---- the prefix index over shared blocks (Engine::restore / Engine::retain, engine.rs:1659-1699) -----
+def test_a_prefix_hit_shares_blocks_in_every_layer_and_eviction_gives_them_back():
+    """lookup -> fork(reuse) -> decode (copy-on-write of the partly filled block, per layer) -> retain the
+    finished sequence -> the budget evicts the oldest entry -> its own blocks return to the free list."""
+    from qubivex_b200.ondevice import OnDevice
+    B, layers, kvh, d = 16, 2, 2, 64
+    od = OnDevice(None, GEO, heads=4, blocks=64)        # bookkeeping only: no device behind it
+    index = od.retain_prefixes(budget_blocks=14)
+    host = lambda n: (np.zeros((kvh, n, d), np.float32), np.zeros((kvh, n, d), np.float32))
+    # a conversation of 40 tokens: positions 0..39, three blocks per layer (the third holds 8 positions)
+    tokens = np.arange(1000, 1040, dtype=np.uint32)
+    owner = od.new_mirror()
+    for l in range(layers):
+        plan_ok(od.kv, [owner], [39], layer=l)
+    k, v = host(40)
+    k[:] = 7.0
+    assert od.retain("s", tokens, owner, k, v) and index.cost() == 6 and od.kv.stats().free == 64 - 6
+    # a request that shares 36 tokens: 2 full blocks + 4 positions of the third, in both layers
+    prompt = np.concatenate([tokens[:36], np.array([5, 6, 7], dtype=np.uint32)])
+    rk, rv = host(64)
+    assert od.restore("other scope", prompt, rk, rv) == (None, 0)
+    m, reuse = od.restore("s", prompt, rk, rv)
+    assert reuse == 36 and od.kv.stats().free == 64 - 6 and float(rk[0, 35, 0]) == 7.0 and float(rk[0, 36, 0]) == 0.0
+    assert [m.synced(l) for l in range(layers)] == [36, 36]
+    for l in range(layers):
+        p = od.kv.attention_plan([m], [36], l)
+        assert len(p.sync_to) == 0                                   # the pool already holds 0..35
+        assert len(p.copy_src) == 1 and p.copy_src[0] == owner_block(od, index, "s", tokens, l, 2)
+        od.kv.commit(p, [m], l)
+        od.kv.free_plan(p)
+    assert od.kv.stats().cow_copies == 2 and od.kv.stats().free == 64 - 8
+    for pos in (37, 38):
+        for l in range(layers):
+            assert len(plan_ok(od.kv, [m], [pos], layer=l).copy_src) == 0
+    # the finished request is retained too: 6 + 6 blocks fit the budget of 14 ...
+    full = np.concatenate([prompt, np.array([9], dtype=np.uint32)])[:39]
+    assert od.retain("s", full, m, rk, rv) and index.stats().entries == 2 and index.cost() == 12
+    # ... a third conversation of 3 blocks per layer does not: the oldest entry goes, and the two blocks per layer
+    # nobody else shares return to the free list (its third block of each layer; the first two the second entry holds)
+    other = od.new_mirror()
+    for l in range(layers):
+        plan_ok(od.kv, [other], [40], layer=l)
+    free_before = od.kv.stats().free
+    ok, ov = host(41)
+    assert od.retain("s", np.arange(5000, 5041, dtype=np.uint32), other, ok, ov)
+    assert index.stats().evicted == 1 and index.stats().entries == 2
+    assert od.kv.stats().free == free_before + 2
+    od.close()                                                       # clears the index: everything comes back
+    
+
+def owner_block(od, index, scope, tokens, layer, i):
+    """Block i of layer `layer` of the retained sequence `tokens` names (looked up, not remembered)."""
+    kept, _, hit = index.lookup(scope, np.concatenate([tokens, np.array([1], dtype=np.uint32)]))
+    try:
+        return int(kept.mirror.blocks(layer)[i])
+    finally:
+        index.release(hit)
+
+
+def test_four_threads_share_one_pool():
+    """crates/qubivex-runtime/tests/discrete.rs:772-801 (concurrent_requests_with_decode_attention): four request
+    threads plan, commit, fork and drop on one pool; afterwards every block is free again."""
+    import threading
+    pool = KvPool(GEO, 256)
+    errors = []
+
+    def request(seed):
+        try:
+            rng = np.random.default_rng(seed)
+            for _ in range(30):
+                m = pool.mirror()
+                n = int(rng.integers(1, 120))
+                for pos in range(n - 1, n + 6):
+                    p = pool.attention_plan([m], [pos], 0)
+                    if p is None:                       # the pool ran dry under the others: declined, nothing broken
+                        break
+                    assert p.pos.tolist() == [pos] and len(p.blocks) == pos // 16 + 1
+                    pool.commit(p, [m], 0)
+                    pool.free_plan(p)
+                child = m.fork(n // 2)
+                m.drop()
+                p = pool.attention_plan([child], [n // 2], 0)
+                if p is not None:
+                    pool.commit(p, [child], 0)
+                    pool.free_plan(p)
+                child.drop()
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=request, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    s = pool.stats()
+    assert s.free == s.blocks == 256 and s.shared_blocks == 0
+    pool.delete()
