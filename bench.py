@@ -36,6 +36,7 @@ from __future__ import annotations
 
 import argparse
 import ctypes as C
+import dataclasses
 import json
 import os
 import subprocess
@@ -442,12 +443,249 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------
+def run_c5(args, rank: int, local_rank: int, world: int) -> None:
+    """The head-sharded configuration: 64 query / 8 KV heads of 128 divided over the ranks by KV head (each
+    rank's pool holds its own heads only; block tables replicated), batch 256, contexts U[1024, 16384], one
+    layer.  A step = append + attention on every rank, each writing into its slot of the gather buffer, then
+    qvx_allgather_heads (ncclAllGather over NVLink + transpose): every rank ends with [token][head][d].
+    Afterwards rank 0 recomputes a few sequences with all eight KV heads on its own GPU and compares the
+    gathered rows of the last step bit for bit."""
+    import torch
+
+    from qubivex_b200 import device as qd
+    from qubivex_b200 import sharding
+    from qubivex_b200.device import ptr
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    dev = qd.CudaDevice(local_rank, timing=4)
+    lib = dev.lib
+    shape = wl.C5
+    s, d, B = shape.batch, shape.head_dim, shape.block_tokens
+    if shape.kv_heads % world:
+        raise SystemExit(f"{shape.kv_heads} KV heads do not divide over {world} ranks")
+    sh = sharding.head_shard(shape.heads, shape.kv_heads, d, rank, world)
+    kvl, hl, group = sh.kv_heads, sh.heads, shape.heads // shape.kv_heads
+    W, K = args.warmup, args.steps
+    scale = wl.value_scale(shape)
+    lengths = wl.contexts(shape, SEED)
+    nb_seq = (lengths + W + K + B - 1) // B
+    n_blocks = int(nb_seq.sum())
+    perm = wl.permutation(n_blocks, SEED)                   # the tables are the same on every rank
+    table_at = np.zeros(s, dtype=np.uint32)
+    table_at[1:] = np.cumsum(nb_seq)[:-1]
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    gen = torch.Generator(device="cuda")
+
+    def seeded(*key):
+        gen.manual_seed(hash((SEED,) + key) & 0x7FFFFFFFFFFFFFFF)
+        return gen
+
+    def context_rows(g: int, t: int) -> "torch.Tensor":
+        """[position][K row | V row] of KV head g of sequence t: what the prefill leaves in the pool."""
+        return torch.randn((int(lengths[t]), 2, d), device="cuda", generator=seeded(1, g, t)) * scale
+
+    def step_inputs(t: int, g: int):
+        """q [s][group][d], k_new [s][d], v_new [s][d] of KV head g at step t."""
+        x = torch.randn((s, group + 2, d), device="cuda", generator=seeded(2, t, g)) * scale
+        return x[:, :group], x[:, group], x[:, group + 1]
+
+    def fill(pool_ptr, geo, pool_blocks, heads_of, seqs, blocks_of, rows_extra=None):
+        """Prefill through the sync path: the context rows of the KV heads `heads_of` of sequences `seqs`."""
+        for j, t in enumerate(seqs):
+            n = int(lengths[t])
+            rows = torch.stack([context_rows(g, t) for g in heads_of], dim=2)          # [n][2][heads][d]
+            rows = rows.reshape(n, 2 * len(heads_of) * d).contiguous()
+            p = np.arange(n)
+            to = (blocks_of(j)[p // B].astype(np.int64) * B + p % B).astype(np.uint32)
+            d_to = torch.from_numpy(to.view(np.int32)).cuda()
+            dev.check(lib.qvx_kv_sync(dev.h, C.byref(geo), pool_ptr, pool_blocks, ptr(rows), ptr(d_to), n, stream))
+        torch.cuda.synchronize()
+
+    geo = qd.geometry(B, kvl, d, qd.BF16, qd.LAYOUT_NATIVE)
+    bb = qd.block_bytes(geo)
+    pool = dev.alloc(n_blocks * bb)
+    my_heads = list(range(sh.kv0, sh.kv0 + kvl))
+    fill(C.c_void_p(pool.ptr), geo, n_blocks, my_heads, range(s), lambda t: perm[int(table_at[t]):int(table_at[t]) + int(nb_seq[t])])
+
+    def local_inputs(t: int):
+        parts = [step_inputs(t, g) for g in my_heads]
+        return (torch.cat([p[0] for p in parts], dim=1).contiguous(), torch.cat([p[1] for p in parts], dim=1).contiguous(),
+                torch.cat([p[2] for p in parts], dim=1).contiguous())
+
+    inputs = [local_inputs(t) for t in range(W + K)]
+    tabs = []
+    for t in range(W + K):
+        pos = (lengths + t).astype(np.uint32)
+        h = C.c_void_p()
+        dev.check(lib.qvx_tables_create(dev.h, C.byref(geo), n_blocks, hl, s, ptr(pos), ptr(perm), n_blocks, ptr(table_at), C.byref(h)))
+        tabs.append(h)
+    uid = [sharding.comm_unique_id() if (rank == 0 and world > 1) else None]
+    if dist is not None:
+        dist.broadcast_object_list(uid, src=0)
+    gather = sharding.HeadGather(dev, world, rank, uid[0], max_tokens=s, heads_local=hl, head_dim=d)
+    slot = C.c_void_p(gather.send_slot(s))
+    full = torch.empty((s, shape.heads, d), device="cuda")
+    pool_p = C.c_void_p(pool.ptr)
+
+    def step(t: int):
+        qt, kt, vt = inputs[t]
+        dev.check(lib.qvx_kv_append_attn_decode(dev.h, tabs[t], pool_p, ptr(kt), ptr(vt), ptr(qt), slot, qd.ATTN_AUTO, stream))
+        gather.all_gather(ptr(full), s, stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for t in range(W):
+        step(t)
+    barrier()
+    dev.reset_kernel_times()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_load0 = time.perf_counter()
+    e0.record()
+    for t in range(W, W + K):
+        step(t)
+    e1.record()
+    barrier()
+    clocks = sampler.stop(t_load0, time.perf_counter())
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_total = float(ms.item())
+    kt_ = dev.kernel_times()
+    last_full = full.clone()
+    # the exchange alone: the last step's gather again, bracketed by events (the slot still holds the rank's outputs)
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    g0.record()
+    for _ in range(8):
+        gather.all_gather(ptr(full), s, stream)
+    g1.record()
+    barrier()
+    gather_us = torch.tensor([g0.elapsed_time(g1) * 1e3 / 8], device="cuda")
+    if dist is not None:
+        dist.all_reduce(gather_us, op=dist.ReduceOp.MAX)
+
+    # ---- e2e: the step's q, k_new, v_new from pinned host memory, the gathered result back to the host -----------
+    hq, hk, hv = (torch.empty_like(x, device="cpu").pin_memory() for x in inputs[W + K - 1])
+    for hbuf, x in zip((hq, hk, hv), inputs[W + K - 1]):
+        hbuf.copy_(x)
+    dq, dk, dv = (torch.empty_like(x) for x in inputs[W + K - 1])
+    hfull = torch.empty((s, shape.heads, d), pin_memory=True)
+    t_e2e = min(W + K - 1, W + 7)
+
+    def step_host():
+        dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True); dv.copy_(hv, non_blocking=True)
+        dev.check(lib.qvx_kv_append_attn_decode(dev.h, tabs[W + K - 1], pool_p, ptr(dk), ptr(dv), ptr(dq), slot, qd.ATTN_AUTO, stream))
+        gather.all_gather(ptr(full), s, stream)
+        hfull.copy_(full, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    n_e2e = max(4, min(K, 16))
+    for _ in range(n_e2e):
+        step_host()
+    el = torch.tensor([time.perf_counter() - t0], device="cuda")
+    if dist is not None:
+        dist.all_reduce(el, op=dist.ReduceOp.MAX)
+    e2e_value = s * n_e2e / float(el.item())
+
+    # ---- the check against one GPU: rank 0 recomputes a few sequences with all eight KV heads ------------------
+    check = None
+    if rank == 0:
+        sample = sorted({int(np.argmin(lengths)), int(np.argsort(lengths)[s // 2]), int(np.argmax(lengths))})
+        geo1 = qd.geometry(B, shape.kv_heads, d, qd.BF16, qd.LAYOUT_NATIVE)
+        nb1 = nb_seq[sample]
+        ta1 = np.zeros(len(sample), dtype=np.uint32)
+        ta1[1:] = np.cumsum(nb1)[:-1]
+        blocks1 = np.arange(int(nb1.sum()), dtype=np.uint32)
+        pool1 = dev.alloc(int(nb1.sum()) * qd.block_bytes(geo1))
+        all_heads = list(range(shape.kv_heads))
+        fill(C.c_void_p(pool1.ptr), geo1, int(nb1.sum()), all_heads, sample, lambda j: blocks1[int(ta1[j]):int(ta1[j]) + int(nb1[j])])
+        out1 = torch.empty((len(sample), shape.heads, d), device="cuda")
+        idx = torch.tensor(sample, device="cuda")
+        for t in range(W + K):                                   # every step's rows land as they did in the run; the last one's outputs count
+            parts = [step_inputs(t, g) for g in all_heads]
+            q1 = torch.cat([p[0][idx] for p in parts], dim=1).contiguous()
+            k1 = torch.cat([p[1][idx] for p in parts], dim=1).contiguous()
+            v1 = torch.cat([p[2][idx] for p in parts], dim=1).contiguous()
+            pos1 = (lengths[sample] + t).astype(np.uint32)
+            h = C.c_void_p()
+            dev.check(lib.qvx_tables_create(dev.h, C.byref(geo1), int(nb1.sum()), shape.heads, len(sample), ptr(pos1), ptr(blocks1),
+                                            len(blocks1), ptr(ta1), C.byref(h)))
+            dev.check(lib.qvx_kv_append_attn_decode(dev.h, h, C.c_void_p(pool1.ptr), ptr(k1), ptr(v1), ptr(q1), ptr(out1), qd.ATTN_AUTO, stream))
+            torch.cuda.synchronize()
+            lib.qvx_tables_free(h)
+        got = last_full[idx]
+        same = bool(torch.equal(got.view(torch.int32), out1.view(torch.int32)))
+        check = {"sequences": sample, "contexts": [int(lengths[i]) + W + K for i in sample], "bit_identical": same,
+                 "max_abs_diff": float((got - out1).abs().max()), "what": "rank 0's gathered [token][head][d] rows of the last step against "
+                 "the same steps run with all 8 KV heads on one GPU"}
+        pool1.free()
+
+    attn_launches, attn_ns = kt_["attn"]
+    algo_rank = float(np.mean([wl.algorithmic_bytes(dataclasses.replace(shape, heads=hl, kv_heads=kvl), lengths + t + 1)
+                               for t in range(W, W + K)]))
+    peak, peak_kind = measured_peak_gbs()
+    attn_us = attn_ns / max(attn_launches, 1) / 1e3
+    value = s * K / (ms_total / 1e3)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": shape.name, "layers": 1, "batch": s, "heads": shape.heads, "kv_heads": shape.kv_heads, "head_dim": d,
+                   "block_tokens": B, "context": [shape.ctx_lo, shape.ctx_hi],
+                   "partition": f"by KV head: {kvl} KV head(s) and {hl} query heads per GPU; one ncclAllGather of the outputs per step",
+                   "l2": f"each launch reads {algo_rank / 2**20:.0f} MiB of KV per GPU, once: no flush between iterations"},
+        "roofline": {"bound": "hbm", "kernel": "attn_stream_kernel (paged decode attention), per GPU", "achieved": algo_rank / (attn_us * 1e-6) / 1e9,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": algo_rank / (attn_us * 1e-6) / 1e9 / peak,
+                     "frac_of_8000": algo_rank / (attn_us * 1e-6) / 1e9 / 8000.0, "traffic": None,
+                     "algorithmic_bytes_per_launch": algo_rank, "launch_us": attn_us, "launches_timed": int(attn_launches),
+                     "how": "CUDA events around every 4th attention launch of the timed region (slowest rank not taken: this rank's)"},
+        "gather": {"us_per_step": float(gather_us.item()), "bytes_gathered_per_gpu": s * shape.heads * d * 4,
+                   "what": "ncclAllGather (in place) + transpose, 8 in a row bracketed by CUDA events, slowest rank"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(world * (hq.numel() + hk.numel() + hv.numel()) * 4),
+                "d2h_bytes_per_step": int(world * hfull.numel() * 4),
+                "call": "per rank and step: q, k_new, v_new from pinned host memory, qvx_kv_append_attn_decode into the gather slot, "
+                        "qvx_allgather_heads, the gathered result back to pinned host memory, synchronize"},
+        "check_vs_one_gpu": check,
+        "gpu_launches": int(2 * K),
+        "clocks": clocks,
+        "cpu_baseline": None,
+    }
+    for h in tabs:
+        lib.qvx_tables_free(h)
+    gather.close()
+    pool.free()
+    dev.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--config", choices=["c2", "c5"], default="c2",
+                    help="c2: the MoE-decoder configuration the metric is quoted on, partitioned by sequence (default); "
+                         "c5: the head-sharded configuration, one all-gather per step")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 48 (debugging only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="the K steps are repeated until the timed region lasts this long")
@@ -458,7 +696,7 @@ def main() -> None:
     else:
         if world != args.gpus and world > 1:
             raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-        run_ours(args, rank, local_rank, world)
+        (run_c5 if args.config == "c5" else run_ours)(args, rank, local_rank, world)
 
 
 if __name__ == "__main__":

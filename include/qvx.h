@@ -250,6 +250,38 @@ int32_t qvx_attn_prelude(qvx_device *dev, const qvx_geometry *geo, size_t heads,
 int32_t qvx_block_copy(qvx_device *dev, const qvx_geometry *geo, void *pool, size_t pool_blocks,
                        const uint32_t *src, const uint32_t *dst, size_t n, void *stream);
 
+/* ---- the head-sharded division over the GPUs of one box ----------------------------------- */
+
+/* No counterpart in the reference, which has one device per engine
+ * (crates/qubivex-runtime/src/engine.rs:1290).  Attention of a (token, head) needs nothing from any
+ * other (crates/qubivex-arch/src/lib.rs:1304-1306), so each GPU can hold the pool of some KV heads
+ * only and run the calls above on them unchanged; the single exchange is afterwards: every rank
+ * has [token][its heads][d] and the caller wants [token][head][d].  One rank per GPU, ranks as
+ * processes or as threads of one process; ranks own equal numbers of heads, in rank order.
+ *
+ * qvx_comm_unique_id: rank 0 makes the 128-byte id and the host hands it to the other ranks by
+ * whatever means it has.  qvx_comm_init: every rank, at the same time (it is NCCL's
+ * ncclCommInitRank and blocks until all have called); it also allocates, once, the gather buffer
+ * for ops of up to max_tokens tokens, so that no step allocates.  nranks == 1 needs no id and no
+ * NCCL.  NCCL is loaded at run time (libnccl.so.2): without it these calls return
+ * QVX_ERR_UNSUPPORTED and everything else in this header still works. */
+typedef struct qvx_comm qvx_comm;
+#define QVX_COMM_ID_BYTES 128
+int32_t qvx_comm_unique_id(uint8_t *id_out_host);
+int32_t qvx_comm_init(qvx_device *dev, int32_t nranks, int32_t rank, const uint8_t *id_host, size_t max_tokens,
+                      size_t heads_local, size_t head_dim, qvx_comm **out);
+void qvx_comm_destroy(qvx_comm *comm);
+/* Where this rank's attention launch should write its [s][heads_local][d] outputs (pass it as `out` of
+ * qvx_attn_decode / qvx_kv_append_attn_decode): the rank's own slot of the gather buffer, so that the
+ * all-gather needs no copy in.  NULL if the op is larger than qvx_comm_init provided for. */
+float *qvx_comm_send_slot(qvx_comm *comm, size_t s, size_t heads_local, size_t head_dim);
+/* ncclAllGather (in place, over NVLink) of every rank's slot, then the transpose into out_full
+ * [s][heads_local * nranks][d] (device memory of this GPU), all on `stream`, after whatever wrote the
+ * slot there.  Every rank calls it, with the same s.  Nothing here reads another GPU's memory
+ * directly: NCCL moves the bytes into this GPU's buffer first. */
+int32_t qvx_allgather_heads(qvx_device *dev, qvx_comm *comm, float *out_full, size_t s, size_t heads_local,
+                            size_t head_dim, void *stream);
+
 /* ---- the op as the reference's device sees it, host memory in and out ------------------- */
 
 /* DeviceMoeAttention after the projections, clip, norms and RoPE

@@ -101,6 +101,11 @@ PROTOTYPES = {
     "qvx_kv_append_attn_decode": (C.c_int32, [P, P, P, P, P, P, P, C.c_uint32, P]),
     "qvx_attn_decode_static": (C.c_int32, [P, _GEO, P, C.c_size_t, C.c_size_t, P, P, P, P, C.c_uint32, P, P]),
     "qvx_block_copy": (C.c_int32, [P, _GEO, P, C.c_size_t, P, P, C.c_size_t, P]),
+    "qvx_comm_unique_id": (C.c_int32, [P]),
+    "qvx_comm_init": (C.c_int32, [P, C.c_int32, C.c_int32, P, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(P)]),
+    "qvx_comm_destroy": (None, [P]),
+    "qvx_comm_send_slot": (P, [P, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "qvx_allgather_heads": (C.c_int32, [P, P, P, C.c_size_t, C.c_size_t, C.c_size_t, P]),
     "qvx_paged_attention_host": (C.c_int32, [P, P, _GEO, C.c_size_t, C.c_size_t, P, P, P, P, P, C.c_size_t, P, P, P,
                                              C.c_size_t, P, C.c_uint32]),
     "qvx_paged_attention_host_async": (C.c_int32, [P, P, _GEO, C.c_size_t, C.c_size_t, P, P, P, P, P, C.c_size_t, P,

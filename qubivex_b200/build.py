@@ -30,7 +30,7 @@ if os.environ.get("QVX_LIB"):
     LIB = Path(os.environ["QVX_LIB"]).resolve()
 EXTRA = os.environ.get("QVX_NVCC_EXTRA", "").split()
 
-LINK: list[str] = []
+LINK: list[str] = ["-ldl"]  # NCCL is bound at run time (comm.cu)
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 SOURCES = {
@@ -42,6 +42,7 @@ SOURCES = {
     "attn_static.cu": [],
     "attn_exact.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],
     "attn_prelude.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],
+    "comm.cu": [],
     "runtime.cpp": [],
 }
 

@@ -62,9 +62,49 @@ def merge_heads(gathered) -> np.ndarray:
     return np.ascontiguousarray(g.transpose(1, 0, 2, 3).reshape(s, world * hl, d))
 
 
+def comm_unique_id() -> bytes:
+    """The 128-byte id rank 0 makes and hands to the other ranks (qvx_comm_unique_id)."""
+    import ctypes as C
+
+    from . import _lib
+    buf = (C.c_uint8 * 128)()
+    rc = _lib.load().qvx_comm_unique_id(buf)
+    if rc:
+        raise RuntimeError(_lib.load().qvx_last_error(None).decode())
+    return bytes(buf)
+
+
+class HeadGather:
+    """The exchange of the head-sharded path behind the C ABI: this rank's attention launch writes into
+    `send_slot(s)`; `all_gather` runs ncclAllGather over NVLink and the transpose to [token][head][d] on the
+    given stream.  Device pointers throughout; nothing passes through the host."""
+
+    def __init__(self, device, nranks: int, rank: int, unique_id: bytes | None, max_tokens: int, heads_local: int, head_dim: int):
+        import ctypes as C
+        self.device, self.nranks, self.rank = device, nranks, rank
+        self.heads_local, self.head_dim = heads_local, head_dim
+        self.h = C.c_void_p()
+        idbuf = (C.c_uint8 * 128).from_buffer_copy(unique_id) if unique_id is not None else None
+        device.check(device.lib.qvx_comm_init(device.h, nranks, rank, idbuf, max_tokens, heads_local, head_dim, C.byref(self.h)))
+
+    def send_slot(self, s: int) -> int:
+        p = self.device.lib.qvx_comm_send_slot(self.h, s, self.heads_local, self.head_dim)
+        if not p:
+            raise ValueError(f"{s} tokens are more than the gather buffer was made for")
+        return p
+
+    def all_gather(self, out_full_ptr, s: int, stream=None) -> None:
+        self.device.check(self.device.lib.qvx_allgather_heads(self.device.h, self.h, out_full_ptr, s, self.heads_local, self.head_dim, stream))
+
+    def close(self) -> None:
+        if self.h:
+            self.device.lib.qvx_comm_destroy(self.h)
+            self.h = None
+
+
 def all_gather_heads(out_local, group=None):
-    """The one exchange of the head-sharded path: torch.distributed all-gather of this rank's
-    [token][local head][d] tensor (NCCL over NVLink on GPUs, gloo on CPU ranks), then the
+    """The same exchange through torch.distributed (gloo on CPU ranks: the tests of the slicing and the
+    transpose that need no GPU): all-gather of this rank's [token][local head][d] tensor, then the
     transpose to [token][head][d].  Every rank gets the whole result."""
     import torch
     import torch.distributed as dist
