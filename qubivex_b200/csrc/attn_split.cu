@@ -31,12 +31,12 @@ constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
 
 // Shared memory per CTA: WARPS rings of `stages` stages (a stage = a key tile then a value
-// tile, 16 rows each), the f32 path's query and probability scratch, the mbarriers.  After
+// tile, 16 rows each), the query and probability scratch, the mbarriers.  After
 // the loop every ring is reused for its warp's result (m[8], l[8], acc[8][d]).
 struct SmemPlan {
     uint32_t tile_bytes, stage_bytes, stages, ring_bytes, q_off, p_off, bar_off, total;
 };
-__host__ __device__ inline SmemPlan smem_plan(uint32_t row_bytes, uint32_t d, bool f32path) {
+__host__ __device__ inline SmemPlan smem_plan(uint32_t row_bytes, uint32_t d) {
     SmemPlan p;
     p.tile_bytes = TILE * row_bytes;
     p.stage_bytes = 2 * p.tile_bytes;
@@ -46,9 +46,9 @@ __host__ __device__ inline SmemPlan smem_plan(uint32_t row_bytes, uint32_t d, bo
     p.ring_bytes = p.stages * p.stage_bytes;
     uint32_t off = WARPS * p.ring_bytes;
     p.q_off = off;
-    if (f32path) off += 8 * d * 4;
+    off += 8 * d * 4;
     p.p_off = off;
-    if (f32path) off += WARPS * TILE * 8 * 4;
+    off += WARPS * TILE * 8 * 4;
     p.bar_off = off;
     off += WARPS * 8 * 8;
     p.total = off;
@@ -115,59 +115,8 @@ __device__ __forceinline__ void merge_and_store(const SplitArgs& a, const Item& 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // The merge is latency bound (a few KiB from L2), so it is arranged as two rounds of
-    // independent loads: every chunk's (m, l) into shared memory, then the weighted sums with
-    // 16-byte loads, eight chunks in flight per thread.
-    const uint32_t stride = 8 * d + 16, nch = it.nch;
-    const float* p0 = a.partials + (size_t)it.part0 * stride;
-    float* msm = scratch;             // [nch][8] maxima, then weights
-    float* lsm = scratch + nch * 8;   // [nch][8] row sums
-    float* Lsm = lsm + nch * 8;       // [8]
-    for (uint32_t i = threadIdx.x; i < nch * 16; i += THREADS) {
-        uint32_t c = i >> 4, j = i & 15;
-        float v = __ldcg(p0 + (size_t)c * stride + 8 * d + j);
-        if (j < 8) msm[c * 8 + j] = v; else lsm[c * 8 + j - 8] = v;
-    }
-    __syncthreads();
-    if (threadIdx.x < 8) {
-        const uint32_t h = threadIdx.x;
-        float M = -INFINITY, L = 0.f;
-        for (uint32_t c = 0; c < nch; c++) M = fmaxf(M, msm[c * 8 + h]);
-        for (uint32_t c = 0; c < nch; c++) {
-            float w = ex2(msm[c * 8 + h] - M);
-            msm[c * 8 + h] = w;
-            L = fmaf(lsm[c * 8 + h], w, L);
-        }
-        Lsm[h] = L;
-    }
-    __syncthreads();
-    const uint32_t d4 = d >> 2;
-    for (uint32_t i = threadIdx.x; i < it.nheads * d4; i += THREADS) {
-        const uint32_t h = i / d4, x = (i % d4) * 4;
-        const float* p = p0 + h * d + x;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        uint32_t c = 0;
-        for (; c + 8 <= nch; c += 8) {
-            float4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; u++) v[u] = __ldcg(reinterpret_cast<const float4*>(p + (size_t)(c + u) * stride));
-#pragma unroll
-            for (int u = 0; u < 8; u++) {
-                float w = msm[(c + u) * 8 + h];
-                acc.x = fmaf(v[u].x, w, acc.x); acc.y = fmaf(v[u].y, w, acc.y);
-                acc.z = fmaf(v[u].z, w, acc.z); acc.w = fmaf(v[u].w, w, acc.w);
-            }
-        }
-        for (; c < nch; c++) {
-            float4 v = __ldcg(reinterpret_cast<const float4*>(p + (size_t)c * stride));
-            float w = msm[c * 8 + h];
-            acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);
-            acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
-        }
-        const float L = Lsm[h];
-        float4 o = make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
-        *reinterpret_cast<float4*>(a.out + ((size_t)it.seq * a.heads + it.head0 + h) * d + x) = o;
-    }
+    merge_chunks_in_order(a.partials + (size_t)it.part0 * (8 * d + 16), it.nch, it.nheads, d,
+                          a.out + ((size_t)it.seq * a.heads + it.head0) * d, scratch, THREADS);
     if (threadIdx.x == 0) a.counters[it.counter] = 0;  // ready for the next launch
 }
 
@@ -179,7 +128,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NJ = NH / 2;   // heads per lane in the score phase
     constexpr int DK = D / 32;   // output dims per lane
-    const SmemPlan sp = smem_plan(D * 4, D, true);
+    const SmemPlan sp = smem_plan(D * 4, D);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t* itw = a.items + (size_t)blockIdx.x * a.item_words;
     const Item it = load_item(itw);
@@ -399,7 +348,7 @@ int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, cons
     a.block_bytes = L.block_bytes; a.page_bytes = L.page_bytes; a.row_bytes = L.row_bytes;
     a.tiles_per_block = L.B / TILE; a.heads = (uint32_t)t->heads; a.d = L.d; a.item_words = t->item_words;
     a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;
-    const SmemPlan sp = smem_plan(L.row_bytes, L.d, true);
+    const SmemPlan sp = smem_plan(L.row_bytes, L.d);
     const unsigned grid = (unsigned)t->n_items;
     const size_t group = t->heads / L.kvh;
     int32_t rc = QVX_ERR_UNSUPPORTED;

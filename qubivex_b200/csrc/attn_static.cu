@@ -130,9 +130,6 @@ __global__ void __launch_bounds__(STHREADS, 3) attn_static_kernel(StaticArgs a) 
     for (int mt = 0; mt < D / 16; mt++) { o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     bool failed = false;
-    const uint32_t mid = lane >> 3, r8 = lane & 7;
-    const uint32_t k_row = r8 + 8 * (mid & 1), k_chunk = mid >> 1;
-    const uint32_t v_row = r8 + 8 * (mid >> 1), v_chunk = mid & 1;
 
     for (uint32_t i = 0; i < n_my; i++) {
         const uint32_t st = i % SM::stages;
@@ -140,49 +137,7 @@ __global__ void __launch_bounds__(STHREADS, 3) attn_static_kernel(StaticArgs a) 
         const uint32_t kt = ring + st * SM::stage_bytes, vt = kt + SM::tile_bytes;
         const uint32_t tau = warp + SW * i;
         const uint32_t valid = min((uint32_t)TILE, tokens - tau * TILE);
-        float sc[4] = {0.f, 0.f, 0.f, 0.f}, sr[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ks++) {
-            uint32_t af[4];
-            ldmatrix_x4(kt + k_row * (D * 2) + (((2 * ks + k_chunk) ^ (k_row & 7)) << 4), af);
-            mma_16816<DT>(sc, af, qf[ks][0], qf[ks][1]);
-            if constexpr (PRECISE) mma_16816<DT>(sr, af, ql[ks][0], ql[ks][1]);
-        }
-        if constexpr (PRECISE) { sc[0] += sr[0]; sc[1] += sr[1]; sc[2] += sr[2]; sc[3] += sr[3]; }
-        if (valid < TILE) {
-            if (g >= valid) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
-            if (g + 8 >= valid) { sc[2] = -INFINITY; sc[3] = -INFINITY; }
-            for (uint32_t c = valid * (D * 2 / 16) + lane; c < TILE * (D * 2 / 16); c += 32)
-                *reinterpret_cast<uint4*>(smem + (vt - sbase) + c * 16) = make_uint4(0, 0, 0, 0);
-            __syncwarp();
-        }
-        float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
-#pragma unroll
-        for (int sh = 4; sh <= 16; sh <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
-        }
-        const float mn0 = fmaxf(m0, mx0 * a.scale_log2), mn1 = fmaxf(m1, mx1 * a.scale_log2);
-        const float al0 = ex2(m0 - mn0), al1 = ex2(m1 - mn1);
-        m0 = mn0; m1 = mn1;
-        const float p0 = ex2(fmaf(sc[0], a.scale_log2, -mn0)), p1 = ex2(fmaf(sc[1], a.scale_log2, -mn1));
-        const float p2 = ex2(fmaf(sc[2], a.scale_log2, -mn0)), p3 = ex2(fmaf(sc[3], a.scale_log2, -mn1));
-        l0 = fmaf(l0, al0, p0 + p2);
-        l1 = fmaf(l1, al1, p1 + p3);
-        uint32_t ph0, pl0, ph1, pl1;
-        split16<DT>(p0, p1, ph0, pl0);
-        split16<DT>(p2, p3, ph1, pl1);
-        const uint32_t pb0 = movmatrix_trans(ph0), pb1 = movmatrix_trans(ph1);
-        uint32_t pc0 = 0, pc1 = 0;
-        if constexpr (PRECISE) { pc0 = movmatrix_trans(pl0); pc1 = movmatrix_trans(pl1); }
-#pragma unroll
-        for (int mt = 0; mt < D / 16; mt++) {
-            o[mt][0] *= al0; o[mt][1] *= al1; o[mt][2] *= al0; o[mt][3] *= al1;
-            uint32_t vf[4];
-            ldmatrix_x4_trans(vt + v_row * (D * 2) + (((2 * mt + v_chunk) ^ (v_row & 7)) << 4), vf);
-            mma_16816<DT>(o[mt], vf, pb0, pb1);
-            if constexpr (PRECISE) mma_16816<DT>(o[mt], vf, pc0, pc1);
-        }
+        attend_tile<DT, D, (PRECISE ? 3 : 0)>(kt, vt, smem + (vt - sbase), valid, lane, qf, ql, a.scale_log2, o, m0, m1, l0, l1);
         __syncwarp();
         if (i + SM::stages < n_my) issue(i + SM::stages);
     }
@@ -235,42 +190,10 @@ __global__ void __launch_bounds__(STHREADS, 3) attn_static_kernel(StaticArgs a) 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // The last chunk of this (sequence, group) to arrive: merge all of them, in chunk order.
-    const float* p0 = a.partials + (size_t)pair * a.max_chunks * PS;
-    float* msm = reinterpret_cast<float*>(smem);  // [nch][8] maxima then weights, [nch][8] sums, [8]: nch <= max_chunks <= 1000 fits the rings
-    float* lsm = msm + nch * 8;
-    float* Lsm = lsm + nch * 8;
-    for (uint32_t i = threadIdx.x; i < nch * 16; i += STHREADS) {
-        const uint32_t c = i >> 4, j = i & 15;
-        const float v = __ldcg(p0 + (size_t)c * PS + 8 * D + j);
-        if (j < 8) msm[c * 8 + j] = v; else lsm[c * 8 + j - 8] = v;
-    }
-    __syncthreads();
-    if (threadIdx.x < 8) {
-        const uint32_t h = threadIdx.x;
-        float M = -INFINITY, L = 0.f;
-        for (uint32_t c = 0; c < nch; c++) M = fmaxf(M, msm[c * 8 + h]);
-        for (uint32_t c = 0; c < nch; c++) {
-            const float w = ex2(msm[c * 8 + h] - M);
-            msm[c * 8 + h] = w;
-            L = fmaf(lsm[c * 8 + h], w, L);
-        }
-        Lsm[h] = L;
-    }
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < nheads * (D / 4); i += STHREADS) {
-        const uint32_t h = i / (D / 4), x = (i % (D / 4)) * 4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t c = 0; c < nch; c++) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(p0 + (size_t)c * PS + h * D + x));
-            const float w = msm[c * 8 + h];
-            acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);
-            acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
-        }
-        const float L = Lsm[h];
-        *reinterpret_cast<float4*>(a.out + ((size_t)seq * a.heads + head0 + h) * D + x) =
-            make_float4(acc.x / L, acc.y / L, acc.z / L, acc.w / L);
-    }
+    // The last chunk of this (sequence, group) to arrive: merge all of them, in chunk order.  The maxima, weights
+    // and sums of nch <= max_chunks <= 1000 chunks ((16 nch + 8) floats) fit the rings, which are free by now.
+    merge_chunks_in_order(a.partials + (size_t)pair * a.max_chunks * PS, nch, nheads, D,
+                          a.out + ((size_t)seq * a.heads + head0) * D, reinterpret_cast<float*>(smem), STHREADS);
 }
 
 extern int* device_status_word(qvx_device* dev);

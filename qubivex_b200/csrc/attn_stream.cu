@@ -70,9 +70,6 @@ constexpr int REC_SLOTS = 4;
 #ifndef QVX_BF16_PASSES
 #define QVX_BF16_PASSES 3   // bf16 pools: 3 = queries and probabilities as value + remainder, 1 = the queries only
 #endif
-#ifndef QVX_LAZY_RESCALE
-#define QVX_LAZY_RESCALE 1
-#endif
 #ifndef QVX_PF_DIST
 #define QVX_PF_DIST 0    // tiles the producer asks into the L2 ahead of the tile it copies into the ring (0: none)
 #endif
@@ -812,9 +809,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
 
     // ================================ consumers ================================
     const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t mid = lane >> 3, r8 = lane & 7;
-    const uint32_t k_row = r8 + 8 * (mid & 1), k_chunk = mid >> 1;  // keys: A = K
-    const uint32_t v_row = r8 + 8 * (mid >> 1), v_chunk = mid & 1;  // values: A = V^T (ldmatrix.trans)
     float* res_all = reinterpret_cast<float*>(smem + SM::res_off);
     uint32_t nbase = 0;   // tiles of the items before this one
     Tracer tr(a.trace_id, warp == 0 ? 2 : 3, lane == 0 && (warp == 0 || warp == CW - 1));
@@ -906,63 +900,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 const uint32_t kt = sbase + SM::ring_off + st * SM::stage_bytes, vt = kt + SM::tile_bytes;
                 const uint32_t valid = min((uint32_t)TILE, ctokens - tau * TILE);
 #if !(defined(QVX_EXPERIMENTS) && defined(QVX_EXPERIMENT_NOCOMPUTE))
-                // S^T = K Q^T; the value pass and the remainder pass accumulate separately so the
-                // chain of dependent tensor-core ops is half as long.
-                float sc[4] = {0.f, 0.f, 0.f, 0.f}, sr[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ks++) {
-                    uint32_t af[4];
-                    ldmatrix_x4(kt + k_row * (D * 2) + (((2 * ks + k_chunk) ^ (k_row & 7)) << 4), af);
-                    mma_16816<DT>(sc, af, qf[ks][0], qf[ks][1]);
-                    if constexpr (PRECISE & 1) mma_16816<DT>(sr, af, ql[ks][0], ql[ks][1]);
-                }
-                if constexpr (PRECISE & 1) { sc[0] += sr[0]; sc[1] += sr[1]; sc[2] += sr[2]; sc[3] += sr[3]; }
-                if (valid < TILE) {
-                    // The tail of the last block: unwritten slots hold whatever the pool held before.
-                    if (g >= valid) { sc[0] = -INFINITY; sc[1] = -INFINITY; }
-                    if (g + 8 >= valid) { sc[2] = -INFINITY; sc[3] = -INFINITY; }
-                    // 0 * NaN is NaN: clear the value rows no probability reaches.
-                    for (uint32_t c = valid * (D * 2 / 16) + lane; c < TILE * (D * 2 / 16); c += 32)
-                        *reinterpret_cast<uint4*>(smem + SM::ring_off + st * SM::stage_bytes + SM::tile_bytes + c * 16) =
-                            make_uint4(0, 0, 0, 0);
-                    fence_proxy_async();  // these generic writes precede the bulk copy that reuses the stage
-                    __syncwarp();
-                }
-                // Online softmax in base 2; this lane sees heads 2t, 2t+1 at positions g, g+8.
-                float mx0 = fmaxf(sc[0], sc[2]), mx1 = fmaxf(sc[1], sc[3]);
-#pragma unroll
-                for (int sh = 4; sh <= 16; sh <<= 1) {
-                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
-                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
-                }
-                const float mn0 = fmaxf(m0, mx0 * a.scale_log2), mn1 = fmaxf(m1, mx1 * a.scale_log2);
-                const float al0 = ex2(m0 - mn0), al1 = ex2(m1 - mn1);
-                m0 = mn0; m1 = mn1;
-                const float p0 = ex2(fmaf(sc[0], a.scale_log2, -mn0)), p1 = ex2(fmaf(sc[1], a.scale_log2, -mn1));
-                const float p2 = ex2(fmaf(sc[2], a.scale_log2, -mn0)), p3 = ex2(fmaf(sc[3], a.scale_log2, -mn1));
-                l0 = fmaf(l0, al0, p0 + p2);
-                l1 = fmaf(l1, al1, p1 + p3);
-                // P^T as the B operand: (position g; heads 2t,2t+1) -> (head g; positions 2t,2t+1).
-                uint32_t ph0, pl0, ph1, pl1;
-                split16<DT>(p0, p1, ph0, pl0);
-                split16<DT>(p2, p3, ph1, pl1);
-                const uint32_t pb0 = movmatrix_trans(ph0), pb1 = movmatrix_trans(ph1);
-                uint32_t pc0 = 0, pc1 = 0;
-                if constexpr (PRECISE & 2) { pc0 = movmatrix_trans(pl0); pc1 = movmatrix_trans(pl1); }
-                // O^T = O^T * alpha + V^T P^T
-                // The running maxima settle after a sequence's first tiles: when no lane's moved, every factor is 1
-                // and the multiplications below are left out (x * 1.0f is x: the bits are the same either way).
-                const bool rescale = QVX_LAZY_RESCALE ? __any_sync(0xffffffffu, al0 != 1.0f || al1 != 1.0f) : true;
-#pragma unroll
-                for (int mt = 0; mt < D / 16; mt++) {
-                    if (rescale) { o[mt][0] *= al0; o[mt][1] *= al1; o[mt][2] *= al0; o[mt][3] *= al1; }
-                    uint32_t vf[4];
-                    ldmatrix_x4_trans(vt + v_row * (D * 2) + (((2 * mt + v_chunk) ^ (v_row & 7)) << 4), vf);
-                    mma_16816<DT>(o[mt], vf, pb0, pb1);
-                    if constexpr (PRECISE & 2) mma_16816<DT>(o[mt], vf, pc0, pc1);
-                }
+                attend_tile<DT, D, PRECISE>(kt, vt, smem + SM::ring_off + st * SM::stage_bytes + SM::tile_bytes, valid, lane, qf, ql,
+                                            a.scale_log2, o, m0, m1, l0, l1);
 #else
-                (void)kt; (void)vt; (void)valid; (void)k_row; (void)k_chunk; (void)v_row; (void)v_chunk;
+                (void)kt; (void)vt; (void)valid;
 #endif
                 __syncwarp();  // every lane is done with this stage
                 if (lane == 0) mbar_arrive(empty0 + st * 8);

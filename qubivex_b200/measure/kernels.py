@@ -1,5 +1,5 @@
 """CUDA-event times of every kernel of the path on the benchmark configurations' shapes, through
-the C ABI, with the algorithmic bytes each moves: `python -m qubivex_b200.profile_kernels [names]`.
+the C ABI, with the algorithmic bytes each moves: `python -m qubivex_b200.measure.kernels [names]`.
 
   c2   one layer of the MoE-decoder shape (batch 64, contexts U[1024, 4096])
   c3   16 x 32768 positions, 8 sequences sharing an 8192-position prefix (shared blocks counted once)
@@ -8,6 +8,9 @@ the C ABI, with the algorithmic bytes each moves: `python -m qubivex_b200.profil
   c1   the f32 reference-runnable shape (split and exact-order kernels)
   rows the sync / append kernel at prefill and decode sizes
   static  the fixed-scratch entry point (qvx_attn_decode_static) on the c2 launch
+  f32  the f32 split kernel at size (batch 64, contexts U[1024, 4096], 8 q / 2 kv heads of 64)
+  copy  block copies at a size a profiler can hold (1474 moves of 128 KiB in a 2 GiB pool)
+  prelude  clip + Q/K norms + RoPE on 64 tokens of the MoE-decoder shape
 """
 from __future__ import annotations
 
@@ -17,9 +20,9 @@ import sys
 import numpy as np
 import torch
 
-from . import device as qd
-from . import workload as wl
-from .device import ptr
+from .. import device as qd
+from .. import workload as wl
+from ..device import ptr
 
 PEAK = 6540.5  # GB/s, measured copy bandwidth of the pool's B200s
 
@@ -149,6 +152,22 @@ def copy_case(dev, name, shape: wl.Shape, pool_blocks, moves):
     _report(name, 2 * moves * bb, sec)
 
 
+def prelude_case(dev, name, shape: wl.Shape):
+    from .._lib import Prelude
+    geo = qd.geometry(shape.block_tokens, shape.kv_heads, shape.head_dim, qd.BF16, qd.LAYOUT_NATIVE)
+    s, d = shape.batch, shape.head_dim
+    q = torch.randn((s, shape.heads, d), device="cuda")
+    k = torch.randn((s, shape.kv_out), device="cuda")
+    v = torch.randn((s, shape.kv_out), device="cuda")
+    rope = torch.randn((s, d), device="cuda")
+    qn, kn = torch.ones(shape.heads * d, device="cuda"), torch.ones(shape.kv_out, device="cuda")
+    pre = Prelude(1, 8.0, qn.data_ptr(), kn.data_ptr(), 1e-6, rope.data_ptr())
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    sec = _time(dev, lambda: dev.check(dev.lib.qvx_attn_prelude(dev.h, C.byref(geo), shape.heads, s, ptr(q), ptr(k), ptr(v), C.byref(pre), stream)),
+                "prelude")
+    _report(name, 2 * 4 * s * (shape.heads * d + 2 * shape.kv_out) + 4 * s * d, sec)
+
+
 def main(names):
     dev = qd.CudaDevice(0, timing=1)
     rng = np.random.default_rng(7)
@@ -172,6 +191,13 @@ def main(names):
         attention_case(dev, "c1 exact f32 (reference order)", wl.C1, [101, 192, 319, 576], dtype=qd.F32, variant=qd.ATTN_EXACT)
         big = wl.Shape("f32-big", 8, 2, 64, 16, "f32", 64, 1024, 4096)
         attention_case(dev, "split f32 at size: batch 64, ctx U[1024,4096], 8q/2kv d64", big, rng.integers(1024, 4097, size=64), dtype=qd.F32)
+    if "f32" in names:
+        big = wl.Shape("f32-big", 8, 2, 64, 16, "f32", 64, 1024, 4096)
+        attention_case(dev, "split f32 at size: batch 64, ctx U[1024,4096], 8q/2kv d64", big, rng.integers(1024, 4097, size=64), dtype=qd.F32)
+    if "copy" in names:
+        copy_case(dev, "block copy: 1474 moves of 128 KiB in a 16384-block pool", wl.C4, 16384, 1474)
+    if "prelude" in names:
+        prelude_case(dev, "attention prelude: 64 tokens, 32q/4kv x 128 (clip, norms, RoPE)", wl.C2)
     if "rows" in names:
         rows_case(dev, "kv sync (prefill): 65536 rows, 4kv x 128, bf16", wl.C2, 65536)
         rows_case(dev, "kv append (decode): 64 rows, 4kv x 128, bf16", wl.C2, 64)

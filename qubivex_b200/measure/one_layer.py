@@ -1,7 +1,7 @@
 """One layer of the MoE-decoder configuration: 25 launches of the decode-attention kernel through
 the C ABI with its CUDA-event time.  The command ncu profiles (see profiles/).
 
-Environment: BATCH, CTX (fixed context), BT (block tokens), PERM=seq|random, QVX_CHUNK_TOKENS."""
+Environment: BATCH, CTX (fixed context), BT (block tokens), PERM=seq|random."""
 import ctypes as C
 import os
 import sys
@@ -10,7 +10,7 @@ import time
 import numpy as np
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from qubivex_b200 import device as qd
 from qubivex_b200 import workload as wl
 from qubivex_b200.device import ptr
