@@ -620,3 +620,72 @@ def test_control_duplicate_sync_rows_written_in_the_other_order_are_noticed(dev)
     bad_pool, bad_want = c.run_oracle()
     assert not np.array_equal(got_pool, bad_pool)                    # the earlier duplicate won there: the bytes differ
     assert not within(got, bad_want, "bf16")[0]
+
+
+# ---- the benchmark configurations at their full sizes, sampled against the oracle ----------------------
+def _full_size_case(name):
+    rng = np.random.default_rng(8)
+    if name == "c3":    # 16 x 32768 positions, 32 q / 4 kv heads of 128, block 16 (the prefix sharing is in test_gpu_scenarios)
+        return 32, 4, 128, 16, np.full(16, 32768)
+    if name == "c4":    # ~58 982 live blocks of 32 positions, 32 q / 8 kv heads: the work items are runs of four chunks
+        lens = []
+        while sum((n + 31) // 32 for n in lens) < 58982:
+            lens.append(int(rng.integers(256, 8193)))
+        return 32, 8, 128, 32, np.array(lens)
+    if name == "c5":    # one GPU's KV head of the head-sharded shape: batch 256, contexts U[1024, 16384] (runs of two chunks)
+        return 8, 1, 128, 16, rng.integers(1024, 16385, size=256)
+    raise ValueError(name)
+
+
+@pytest.mark.parametrize("name", ["c3", "c4", "c5"])
+def test_full_size_configurations_sampled_against_the_oracle(dev, name):
+    """One attention step at the configuration's full size (up to 7.2 GiB of KV, hundreds of work items per CTA, runs of
+    two to four chunks, merge trees of two levels), and the shortest, the median and the longest sequence checked against
+    the oracle on their own blocks of the pool."""
+    torch = pytest.importorskip("torch")
+    import ctypes as C
+    from qubivex_b200.device import ptr
+    heads, kvh, d, B, lengths = _full_size_case(name)
+    lengths = np.asarray(lengths, dtype=np.int64)
+    s = len(lengths)
+    geo = qd.geometry(B, kvh, d, qd.BF16)
+    bb = qd.block_bytes(geo)
+    nb = (lengths + B - 1) // B
+    pool_blocks = int(nb.sum()) + 16
+    perm = np.random.default_rng(9).permutation(pool_blocks).astype(np.uint32)
+    table_at = np.zeros(s, dtype=np.uint32)
+    table_at[1:] = np.cumsum(nb)[:-1]
+    blocks = perm[: int(nb.sum())].copy()
+    pos = (lengths - 1).astype(np.uint32)
+    g = torch.Generator(device="cuda").manual_seed(10)
+    pool = torch.empty(pool_blocks * bb // 2, dtype=torch.bfloat16, device="cuda")
+    step = 1 << 28
+    for lo in range(0, pool.numel(), step):                      # N(0,1) / sqrt(d), written as bf16 bits
+        n = min(step, pool.numel() - lo)
+        pool[lo:lo + n] = (torch.randn(n, device="cuda", generator=g) * d ** -0.5).to(torch.bfloat16)
+    q = torch.randn((s, heads, d), device="cuda", generator=g) * d ** -0.5
+    out = torch.empty_like(q)
+    tabs = C.c_void_p()
+    dev.check(dev.lib.qvx_tables_create(dev.h, C.byref(geo), pool_blocks, heads, s, ptr(pos), ptr(blocks), len(blocks), ptr(table_at),
+                                        C.byref(tabs)))
+    dev.check(dev.lib.qvx_attn_decode(dev.h, tabs, ptr(pool), ptr(q), ptr(out), qd.ATTN_SPLIT,
+                                      C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    dev.kernel_times()
+    dev.lib.qvx_tables_free(tabs)
+    assert bool(torch.isfinite(out).all())
+    geo_o = oracle.geometry(B, kvh, d, oracle.BF16)
+    order = np.argsort(lengths)
+    bytes_view = pool.view(torch.uint8)
+    for t in {int(order[0]), int(order[s // 2]), int(order[-1])}:
+        ids = blocks[int(table_at[t]):int(table_at[t]) + int(nb[t])].astype(np.int64)
+        idx = (torch.from_numpy(ids).cuda()[:, None] * bb + torch.arange(bb, device="cuda")[None, :]).reshape(-1)
+        host_pool = bytes_view[idx].cpu().numpy()
+        rc, want = oracle.attn_decode(host_pool, geo_o, heads, q[t:t + 1].cpu().numpy(), pos[t:t + 1], np.arange(len(ids), dtype=np.uint32),
+                                      np.zeros(1, dtype=np.uint32), threads=8)
+        assert rc == 0
+        ok, err = within(out[t:t + 1].cpu().numpy(), want, "bf16")
+        assert ok, (name, t, int(lengths[t]), err)
+        # the values are ~ 1 / sqrt(d) and the outputs an average of thousands of them: the absolute bar alone would pass
+        # anything, so the relative error against the largest output counts too
+        assert err <= 1e-2 * float(np.abs(want).max()), (name, t, err)

@@ -163,7 +163,8 @@ def test_one_thread_may_drive_two_devices():
         dev = qd.CudaDevice(ordinal)
         try:
             with torch.cuda.device(ordinal):
-                _close(_case(dev, torch, 5 + ordinal, [700, 1025], heads=8, kvh=2))
+                # (a device's first launch loads the kernel and the array that comes with it: no free-memory check)
+                _close(_case(dev, torch, 5 + ordinal, [700, 1025], heads=8, kvh=2, first_launch=True))
             c = Case(8, 2, 64, 16, "f32", [600, 40, 1100], seed=7)   # the f32 split kernel's opt-in as well
             _, want = c.run_oracle()
             _, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
