@@ -531,6 +531,27 @@ def run_c5(args, rank: int, local_rank: int, world: int) -> None:
     if dist is not None:
         dist.broadcast_object_list(uid, src=0)
     gather = sharding.HeadGather(dev, world, rank, uid[0], max_tokens=s, heads_local=hl, head_dim=d)
+    # The exchange over peer memory where the GPUs reach each other's memory (stores and flags over NVLink, no NCCL call
+    # per step); a second communicator stays on NCCL so that both are timed.
+    gather_nccl, peer_note = None, "one GPU: nothing to exchange"
+    if dist is not None:
+        peer_note = "ncclAllGather (in place) + transpose"
+        if args.gather == "peer":
+            try:
+                handles = [None] * world
+                dist.all_gather_object(handles, gather.peer_handle())
+                gather.peer_open(handles)
+                peer_note = "peer memory: each rank stores its rows into every rank's buffer over NVLink, flags, bounded wait, copy out"
+            except Exception as e:  # noqa: BLE001 -- no peer access between these devices: NCCL serves
+                peer_note += f" (peer memory not available: {e})"
+            ok = torch.tensor([1 if gather.over_peer_memory else 0], device="cuda")
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if not int(ok.item()) and gather.over_peer_memory:
+                raise SystemExit("peer memory opened on some ranks only")
+        if gather.over_peer_memory:
+            uid2 = [sharding.comm_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(uid2, src=0)
+            gather_nccl = sharding.HeadGather(dev, world, rank, uid2[0], max_tokens=s, heads_local=hl, head_dim=d)
     slot = C.c_void_p(gather.send_slot(s))
     full = torch.empty((s, shape.heads, d), device="cuda")
     pool_p = C.c_void_p(pool.ptr)
@@ -575,6 +596,21 @@ def run_c5(args, rank: int, local_rank: int, world: int) -> None:
     gather_us = torch.tensor([g0.elapsed_time(g1) * 1e3 / 8], device="cuda")
     if dist is not None:
         dist.all_reduce(gather_us, op=dist.ReduceOp.MAX)
+    nccl_us = None
+    if gather_nccl is not None:                     # the same exchange through NCCL, for comparison (its slot's contents do not matter)
+        for _ in range(3):
+            gather_nccl.all_gather(ptr(full), s, stream)
+        barrier()
+        g0.record()
+        for _ in range(8):
+            gather_nccl.all_gather(ptr(full), s, stream)
+        g1.record()
+        barrier()
+        nccl_us = torch.tensor([g0.elapsed_time(g1) * 1e3 / 8], device="cuda")
+        dist.all_reduce(nccl_us, op=dist.ReduceOp.MAX)
+        nccl_us = float(nccl_us.item())
+        gather.all_gather(ptr(full), s, stream)     # (the result buffer again holds the last step's rows)
+        torch.cuda.synchronize()
 
     # ---- e2e: the step's q, k_new, v_new from pinned host memory, the gathered result back to the host -----------
     hq, hk, hv = (torch.empty_like(x, device="cpu").pin_memory() for x in inputs[W + K - 1])
@@ -654,8 +690,8 @@ def run_c5(args, rank: int, local_rank: int, world: int) -> None:
                      "frac_of_8000": algo_rank / (attn_us * 1e-6) / 1e9 / 8000.0, "traffic": None,
                      "algorithmic_bytes_per_launch": algo_rank, "launch_us": attn_us, "launches_timed": int(attn_launches),
                      "how": "CUDA events around every 4th attention launch of the timed region (slowest rank not taken: this rank's)"},
-        "gather": {"us_per_step": float(gather_us.item()), "bytes_gathered_per_gpu": s * shape.heads * d * 4,
-                   "what": "ncclAllGather (in place) + transpose, 8 in a row bracketed by CUDA events, slowest rank"},
+        "gather": {"us_per_step": float(gather_us.item()), "bytes_gathered_per_gpu": s * shape.heads * d * 4, "path": peer_note,
+                   "nccl_us_per_step": nccl_us, "what": "8 exchanges in a row bracketed by CUDA events, slowest rank"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(world * (hq.numel() + hk.numel() + hv.numel()) * 4),
                 "d2h_bytes_per_step": int(world * hfull.numel() * 4),
                 "call": "per rank and step: q, k_new, v_new from pinned host memory, qvx_kv_append_attn_decode into the gather slot, "
@@ -668,6 +704,8 @@ def run_c5(args, rank: int, local_rank: int, world: int) -> None:
     for h in tabs:
         lib.qvx_tables_free(h)
     gather.close()
+    if gather_nccl is not None:
+        gather_nccl.close()
     pool.free()
     dev.close()
     if dist is not None:
@@ -686,6 +724,8 @@ def main() -> None:
     ap.add_argument("--config", choices=["c2", "c5"], default="c2",
                     help="c2: the MoE-decoder configuration the metric is quoted on, partitioned by sequence (default); "
                          "c5: the head-sharded configuration, one all-gather per step")
+    ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
+                    help="c5: the outputs' exchange over peer memory where the GPUs allow it (default), or through NCCL only")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 48 (debugging only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="the K steps are repeated until the timed region lasts this long")

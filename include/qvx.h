@@ -271,6 +271,18 @@ int32_t qvx_comm_unique_id(uint8_t *id_out_host);
 int32_t qvx_comm_init(qvx_device *dev, int32_t nranks, int32_t rank, const uint8_t *id_host, size_t max_tokens,
                       size_t heads_local, size_t head_dim, qvx_comm **out);
 void qvx_comm_destroy(qvx_comm *comm);
+/* Optional: the same exchange over peer memory, with no NCCL call per step.  Every rank calls
+ * qvx_comm_peer_handle (it allocates the rank's result buffers, once, and describes them in
+ * QVX_COMM_HANDLE_BYTES bytes), the host gathers the nranks handles in rank order and every rank calls
+ * qvx_comm_peer_open with all of them (CUDA IPC between processes, peer access between threads of one
+ * process).  From then on qvx_allgather_heads stores this rank's rows straight into every rank's
+ * buffer over NVLink, already transposed, raises a flag on every rank, waits (bounded: a rank that
+ * never arrives leaves "gave up a bounded wait" in the device status and nothing is handed over) for
+ * every rank's flag and copies the result out.  Stores and flag words only cross GPUs.  If either call
+ * fails (no peer access between the devices), the communicator keeps working over NCCL. */
+#define QVX_COMM_HANDLE_BYTES 128
+int32_t qvx_comm_peer_handle(qvx_comm *comm, uint8_t *handle_out_host);
+int32_t qvx_comm_peer_open(qvx_comm *comm, const uint8_t *handles_host);
 /* Where this rank's attention launch should write its [s][heads_local][d] outputs (pass it as `out` of
  * qvx_attn_decode / qvx_kv_append_attn_decode): the rank's own slot of the gather buffer, so that the
  * all-gather needs no copy in.  NULL if the op is larger than qvx_comm_init provided for. */

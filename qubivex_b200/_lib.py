@@ -104,6 +104,8 @@ PROTOTYPES = {
     "qvx_comm_unique_id": (C.c_int32, [P]),
     "qvx_comm_init": (C.c_int32, [P, C.c_int32, C.c_int32, P, C.c_size_t, C.c_size_t, C.c_size_t, C.POINTER(P)]),
     "qvx_comm_destroy": (None, [P]),
+    "qvx_comm_peer_handle": (C.c_int32, [P, P]),
+    "qvx_comm_peer_open": (C.c_int32, [P, P]),
     "qvx_comm_send_slot": (P, [P, C.c_size_t, C.c_size_t, C.c_size_t]),
     "qvx_allgather_heads": (C.c_int32, [P, P, P, C.c_size_t, C.c_size_t, C.c_size_t, P]),
     "qvx_paged_attention_host": (C.c_int32, [P, P, _GEO, C.c_size_t, C.c_size_t, P, P, P, P, P, C.c_size_t, P, P, P,

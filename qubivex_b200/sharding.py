@@ -96,6 +96,22 @@ class HeadGather:
     def all_gather(self, out_full_ptr, s: int, stream=None) -> None:
         self.device.check(self.device.lib.qvx_allgather_heads(self.device.h, self.h, out_full_ptr, s, self.heads_local, self.head_dim, stream))
 
+    def peer_handle(self) -> bytes:
+        """This rank's result buffers, described in 128 bytes for the other ranks (qvx_comm_peer_handle)."""
+        import ctypes as C
+        buf = (C.c_uint8 * 128)()
+        self.device.check(self.device.lib.qvx_comm_peer_handle(self.h, buf))
+        return bytes(buf)
+
+    def peer_open(self, handles: list[bytes]) -> None:
+        """Every rank's handle, in rank order (qvx_comm_peer_open): from now on all_gather goes over peer memory."""
+        import ctypes as C
+        blob = b"".join(handles)
+        self.device.check(self.device.lib.qvx_comm_peer_open(self.h, (C.c_uint8 * len(blob)).from_buffer_copy(blob)))
+        self.over_peer_memory = True
+
+    over_peer_memory = False
+
     def close(self) -> None:
         if self.h:
             self.device.lib.qvx_comm_destroy(self.h)

@@ -79,10 +79,22 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
     import ctypes as C
     gather.all_gather(C.c_void_p(full.data_ptr()), s, C.c_void_p(torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
+    # the same exchange over peer memory: every rank maps the others' result buffers, then stores and flags only
+    mine = gather.peer_handle()
+    handles = [None] * world
+    dist.all_gather_object(handles, mine)
+    gather.peer_open(handles)
+    peer_ok = True
+    for step in range(5):                                   # several in a row: the two result buffers alternate
+        again = torch.full((s, heads, d), float(step), device="cuda")
+        gather.all_gather(C.c_void_p(again.data_ptr()), s, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        peer_ok = peer_ok and torch.equal(again.view(torch.int32), full.view(torch.int32))
+    dev.kernel_times()                                      # no bounded wait ran out
     if rank == 0:
         want = run(dev, kvh, heads, q, k_new, v_new, sync)
         same = torch.equal(full.view(torch.int32), want.view(torch.int32))
-        np.save(os.path.join(out_dir, "ok.npy"), np.array([same]))
+        np.save(os.path.join(out_dir, "ok.npy"), np.array([same, peer_ok]))
     gather.close()
     dev.close()
     dist.barrier()
@@ -96,4 +108,6 @@ def test_head_sharded_decode_over_two_gpus_equals_one_gpu(tmp_path):
     import torch.multiprocessing as mp
 
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    assert bool(np.load(tmp_path / "ok.npy")[0])
+    ok = np.load(tmp_path / "ok.npy")
+    assert bool(ok[0]), "the NCCL gather differs from one GPU"
+    assert bool(ok[1]), "the peer-memory gather differs from the NCCL gather"
