@@ -397,7 +397,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     # Both variants step over the same positions (the second rewrites the rows the first wrote).
     e2e_pipelined, each_pipelined = time_host(W + K, True)
+    x0 = dev.transfers()
     e2e_value, each_ms = time_host(W + K, False)
+    x1 = dev.transfers()
+    ops = max(1, x1.submissions - x0.submissions)
+    host_us = {"submit_us_per_op": (x1.submit_ns - x0.submit_ns) / ops / 1e3, "wait_us_per_op": (x1.wait_ns - x0.wait_ns) / ops / 1e3,
+               "what": "host time inside qvx_paged_attention_host per layer: queueing the copies and kernels, then waiting for the stream"}
     checksum = float(sum(float(o[0, 0, 0]) for o in oh))
     assert np.isfinite(checksum)
 
@@ -422,7 +427,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                      "kernels_us_per_launch": {k: (v[1] / v[0] / 1e3 if v[0] else 0.0) for k, v in kt.items() if v[0]}},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "call": "qvx_paged_attention_host x layers per step: synchronous, one op per layer, as DiscreteDevice::routed_moe",
-                "ms_each_step": each_ms,
+                "ms_each_step": each_ms, "host": host_us,
                 "pipelined": {"value": e2e_pipelined, "call": "qvx_paged_attention_host_async x layers + qvx_wait per step",
                               "ms_each_step": each_pipelined}},
         "parity_sample": parity,
