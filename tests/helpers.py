@@ -7,7 +7,7 @@ import oracle
 from qubivex_b200 import device as qd
 
 DT = {"f32": 0, "bf16": 1, "f16": 2}
-# north star: max-abs 2e-3 / max-rel 1e-2 for 16-bit KV, 1e-5 for f32.
+# The parity bars: max-abs 2e-3 plus max-rel 1e-2 for 16-bit KV, max-abs 1e-5 for f32.
 TOL = {"f32": (1e-5, 0.0), "bf16": (2e-3, 1e-2), "f16": (2e-3, 1e-2)}
 
 
