@@ -291,6 +291,9 @@ static const uint32_t RUN_TOKENS = 2048;
 #ifndef QVX_SMALL_TOKENS_DEFAULT
 #define QVX_SMALL_TOKENS_DEFAULT 256
 #endif
+#ifndef QVX_SPREAD_DEFAULT
+#define QVX_SPREAD_DEFAULT 1
+#endif
 // An experiment build reads a fixed run length from QVX_RUN_CHUNKS at every op (the tests that show
 // that the run length moves no bit use it); the shipped library always chooses by the rule below.
 static uint32_t run_chunks_override() {
@@ -395,12 +398,13 @@ static void for_each_run(uint32_t nch, uint32_t run, uint32_t tail, F f) {
 // Where the short work items go in the queue: items of fewer than `small_tokens` positions are taken
 // out of the longest-first order and dealt out after the first `small_after` x (resident CTAs) items.
 // The order changes no bit of any result (a chunk's arithmetic does not depend on when it runs).
-struct QueueOrder { uint32_t small_tokens, small_after; };
+struct QueueOrder { uint32_t small_tokens, small_after, spread; };
 static QueueOrder queue_order() {
-    QueueOrder qo{QVX_SMALL_TOKENS_DEFAULT, 0};
+    QueueOrder qo{QVX_SMALL_TOKENS_DEFAULT, 0, QVX_SPREAD_DEFAULT};
 #ifdef QVX_EXPERIMENTS
     if (const char* v = getenv("QVX_SMALL_TOKENS")) qo.small_tokens = (uint32_t)atol(v);
     if (const char* v = getenv("QVX_SMALL_AFTER")) qo.small_after = (uint32_t)atol(v);
+    if (const char* v = getenv("QVX_SPREAD")) qo.spread = (uint32_t)atol(v);
 #endif
     return qo;
 }
@@ -483,7 +487,7 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
     const uint32_t group = (uint32_t)(heads / L.kvh), gpk = (group + 7) / 8, groups = L.kvh * gpk;
     // Longest first, so the short tails fill the end of the launch.  The order is a function
     // of the lengths alone: a counting sort by tokens, ties in (sequence, group, chunk) order.
-    struct Key { uint32_t tokens, seq, grp, c, run; };
+    struct Key { uint32_t tokens, seq, grp, c, run, nch; };
     std::vector<Key> keys;
     keys.reserve(im.n_items);
     std::vector<uint32_t> part_base(s), counter_base(s);
@@ -495,20 +499,28 @@ static void fill_image(const TableImage& im, uint8_t* img, const Layout& L, size
         if (nch > 1) { part += attn_parts_per_group(L, nch) * groups; counter += attn_counters_per_group(L, nch) * groups; }
         for (uint32_t grp = 0; grp < groups; grp++)
             for_each_run(nch, run, run_tail_chunks(), [&](uint32_t c, uint32_t r) {
-                keys.push_back(Key{std::min(len, (c + r) * chunk) - c * chunk, (uint32_t)t, grp, c, r});
+                keys.push_back(Key{std::min(len, (c + r) * chunk) - c * chunk, (uint32_t)t, grp, c, r, nch});
             });
     }
-    // Among items of equal size the early chunks of every sequence go first, then the next chunks of
-    // every sequence, and so on: the chunks of one merge node then arrive rounds apart, not together,
-    // so its last arrival finds the others long published (and folds them while it streams) instead of
-    // eight CTAs finishing a node's chunks at once and one of them waiting for seven publications.
-    std::stable_sort(keys.begin(), keys.end(), [](const Key& a, const Key& b) { return a.c < b.c; });
+    // Among items of equal size a sequence's chunks sit at even distances over the whole queue (chunk c of n at the
+    // fraction c / n of it): the chunks of one merge node then arrive rounds apart, not together, and the queue's
+    // last round holds at most one full chunk of a node -- so a node's last arrival finds the others long published
+    // and folds them while it streams, instead of eight CTAs finishing a node's chunks at once and one of them
+    // waiting for seven publications.  (`spread` 0: chunk 0 of every sequence, then chunk 1 of every sequence, ...,
+    // which bunches a long sequence's last chunks in the last round; 2: by place alone, sizes not looked at.)
+    if (queue_order().spread)
+        std::stable_sort(keys.begin(), keys.end(), [](const Key& a, const Key& b) { return (uint64_t)a.c * b.nch < (uint64_t)b.c * a.nch; });
+    else
+        std::stable_sort(keys.begin(), keys.end(), [](const Key& a, const Key& b) { return a.c < b.c; });
     // (a counting sort: tokens <= max_chunk, and this runs once per op on the host's critical path)
     std::vector<uint32_t> start(max_chunk + 2, 0);
     for (const Key& k : keys) start[max_chunk - k.tokens + 1]++;
     for (uint32_t v = 0; v <= max_chunk; v++) start[v + 1] += start[v];
     std::vector<uint32_t> order(keys.size());
-    for (uint32_t i = 0; i < keys.size(); i++) order[start[max_chunk - keys[i].tokens]++] = i;
+    if (queue_order().spread == 2)
+        for (uint32_t i = 0; i < keys.size(); i++) order[i] = i;  // by place in the sequence alone: sizes are not looked at (the short ones still go first, below)
+    else
+        for (uint32_t i = 0; i < keys.size(); i++) order[start[max_chunk - keys[i].tokens]++] = i;
     // The short items do not go last.  Nearly every short item is a sequence's last, partly filled chunk,
     // and whichever chunk of a sequence finishes last merges the others' results: at the very end of
     // the queue that merge (a few rounds of loads) lasts longer than the item itself and every CTA's exit
