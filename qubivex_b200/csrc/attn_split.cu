@@ -48,7 +48,7 @@ __host__ __device__ inline SmemPlan smem_plan(uint32_t row_bytes, uint32_t d) {
     p.q_off = off;
     off += 8 * d * 4;
     p.p_off = off;
-    off += WARPS * TILE * 8 * 4;
+    off += WARPS * TILE * 8 * 8;   // per warp: [position][8 heads] of (p, p) pairs
     p.bar_off = off;
     off += WARPS * 8 * 8;
     p.total = off;
@@ -122,12 +122,21 @@ __device__ __forceinline__ void merge_and_store(const SplitArgs& a, const Item& 
 
 // ---- f32 pools: CUDA-core path -------------------------------------------------------------
 // Scores: lane = (position = lane & 15, half = lane >> 4) computes heads half, half+2, ...;
-// values: lane owns output dims lane, lane+32, ... of all NH heads.
+// values: lane owns output dims 2 lane, 2 lane + 1 (+ 64, ...) of all NH heads.
+// The kernel is bound by instruction issue, not by memory (every multiply-add takes operands from shared memory),
+// so the multiply-adds go out two at a time (fma.rn.f32x2, a Blackwell instruction): a score is summed as an even
+// and an odd half, an output pair (2 lane, 2 lane + 1) takes one instruction per head and position.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra = *reinterpret_cast<unsigned long long*>(&a), rb = *reinterpret_cast<unsigned long long*>(&b),
+                       rc = *reinterpret_cast<unsigned long long*>(&c), rd;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    return *reinterpret_cast<float2*>(&rd);
+}
 template <int D, int NH>
 __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NJ = NH / 2;   // heads per lane in the score phase
-    constexpr int DK = D / 32;   // output dims per lane
+    constexpr int DK = D / 64;   // output pairs per lane
     const SmemPlan sp = smem_plan(D * 4, D);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t* itw = a.items + (size_t)blockIdx.x * a.item_words;
@@ -161,15 +170,16 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
         qs[i] = h < it.nheads ? a.q[((size_t)it.seq * a.heads + it.head0 + h) * D + x] * a.scale_log2 : 0.f;
     }
     __syncthreads();
-    float* ps = reinterpret_cast<float*>(smem + sp.p_off) + warp * (TILE * 8);  // [position][8]
+    float2* ps = reinterpret_cast<float2*>(smem + sp.p_off) + warp * (TILE * 8);  // [position][8] of (p, p)
 
     const uint32_t tok = lane & 15, half = lane >> 4;
-    float m[NH], o[NH][DK], lpart[NJ];
+    float m[NH], lpart[NJ];
+    float2 o[NH][DK];
 #pragma unroll
     for (int h = 0; h < NH; h++) {
         m[h] = -INFINITY;
 #pragma unroll
-        for (int k = 0; k < DK; k++) o[h][k] = 0.f;
+        for (int k = 0; k < DK; k++) o[h][k] = make_float2(0.f, 0.f);
     }
 #pragma unroll
     for (int j = 0; j < NJ; j++) lpart[j] = 0.f;
@@ -183,20 +193,23 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
         const uint32_t tau = warp + WARPS * i;
         const uint32_t valid = min((uint32_t)TILE, it.tokens - tau * TILE);
 
-        float s[NJ];
+        float2 s2[NJ];
 #pragma unroll
-        for (int j = 0; j < NJ; j++) s[j] = 0.f;
+        for (int j = 0; j < NJ; j++) s2[j] = make_float2(0.f, 0.f);
         const uint8_t* krow = kt + tok * (D * 4);
 #pragma unroll 4
         for (int c = 0; c < D / 4; c++) {
-            float4 kv = *reinterpret_cast<const float4*>(krow + ((c ^ (tok & 7)) << 4));
+            const float4 kv = *reinterpret_cast<const float4*>(krow + ((c ^ (tok & 7)) << 4));
 #pragma unroll
             for (int j = 0; j < NJ; j++) {
-                float4 qv = *reinterpret_cast<const float4*>(qs + (half + 2 * j) * D + 4 * c);
-                s[j] = fmaf(qv.x, kv.x, s[j]); s[j] = fmaf(qv.y, kv.y, s[j]);
-                s[j] = fmaf(qv.z, kv.z, s[j]); s[j] = fmaf(qv.w, kv.w, s[j]);
+                const float4 qv = *reinterpret_cast<const float4*>(qs + (half + 2 * j) * D + 4 * c);
+                s2[j] = fma2(make_float2(qv.x, qv.y), make_float2(kv.x, kv.y), s2[j]);
+                s2[j] = fma2(make_float2(qv.z, qv.w), make_float2(kv.z, kv.w), s2[j]);
             }
         }
+        float s[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) s[j] = s2[j].x + s2[j].y;
         if (tok >= valid) {
 #pragma unroll
             for (int j = 0; j < NJ; j++) s[j] = -INFINITY;
@@ -226,26 +239,42 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
             float al_mine = half == 0 ? al[2 * j] : al[2 * j + 1];
             float p = ex2(s[j] - mine);
             lpart[j] = fmaf(lpart[j], al_mine, p);
-            ps[tok * 8 + half + 2 * j] = p;
+            ps[tok * 8 + half + 2 * j] = make_float2(p, p);
         }
         __syncwarp();
+        bool moved = false;
 #pragma unroll
-        for (int h = 0; h < NH; h++) {
+        for (int h = 0; h < NH; h++) moved = moved || al[h] != 1.0f;
+        if (moved) {   // (the maxima settle after a chunk's first tiles: x * 1.0f is x, so skipping changes no bit)
 #pragma unroll
-            for (int k = 0; k < DK; k++) o[h][k] *= al[h];
+            for (int h = 0; h < NH; h++) {
+#pragma unroll
+                for (int k = 0; k < DK; k++) { o[h][k].x *= al[h]; o[h][k].y *= al[h]; }
+            }
         }
-        for (uint32_t p = 0; p < valid; p++) {
-            float pv[8];
-            *reinterpret_cast<float4*>(pv) = *reinterpret_cast<const float4*>(ps + p * 8);
-            if (NH > 4) *reinterpret_cast<float4*>(pv + 4) = *reinterpret_cast<const float4*>(ps + p * 8 + 4);
+        // This lane's dims 2 lane, 2 lane + 1 (+ 64 k) of a value row: one 8-byte load in the row's swizzled chunk.
+        auto accumulate = [&](uint32_t p) {
+            float2 pv[NH];
+#pragma unroll
+            for (int h = 0; h < NH; h += 2) {
+                const float4 two = *reinterpret_cast<const float4*>(ps + p * 8 + h);
+                pv[h] = make_float2(two.x, two.y);
+                pv[h + 1] = make_float2(two.z, two.w);
+            }
             const uint8_t* vrow = vt + p * (D * 4);
 #pragma unroll
             for (int k = 0; k < DK; k++) {
-                uint32_t x = lane + 32 * k;
-                float v = *reinterpret_cast<const float*>(vrow + ((((x >> 2) ^ (p & 7)) << 4) | ((x & 3) << 2)));
+                const uint32_t chunk = (lane >> 1) + 16u * k;
+                const float2 v = *reinterpret_cast<const float2*>(vrow + (((chunk ^ (p & 7)) << 4) | ((lane & 1u) << 3)));
 #pragma unroll
-                for (int h = 0; h < NH; h++) o[h][k] = fmaf(pv[h], v, o[h][k]);
+                for (int h = 0; h < NH; h++) o[h][k] = fma2(pv[h], v, o[h][k]);
             }
+        };
+        if (valid == TILE) {
+#pragma unroll
+            for (uint32_t p = 0; p < TILE; p++) accumulate(p);
+        } else {
+            for (uint32_t p = 0; p < valid; p++) accumulate(p);   // (rows past `valid` may hold anything, NaNs included)
         }
         __syncwarp();
         if (i + sp.stages < n_my) ts.issue(i + sp.stages);
@@ -278,7 +307,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_split_f32_kernel(SplitArgs a)
 #pragma unroll
     for (int h = 0; h < NH; h++) {
 #pragma unroll
-        for (int k = 0; k < DK; k++) res[16 + h * D + lane + 32 * k] = o[h][k];
+        for (int k = 0; k < DK; k++) *reinterpret_cast<float2*>(res + 16 + h * D + 2 * lane + 64 * k) = o[h][k];
     }
     __syncthreads();
     merge_and_store(a, it, reinterpret_cast<const float*>(smem), res_stride_f, D, reinterpret_cast<float*>(smem));

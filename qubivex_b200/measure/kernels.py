@@ -15,6 +15,7 @@ the C ABI, with the algorithmic bytes each moves: `python -m qubivex_b200.measur
 from __future__ import annotations
 
 import ctypes as C
+import os
 import sys
 
 import numpy as np
@@ -169,7 +170,8 @@ def prelude_case(dev, name, shape: wl.Shape):
 
 
 def main(names):
-    dev = qd.CudaDevice(0, timing=1)
+    # QVX_MEASURE_EXPERIMENTS=1: the experiment build of the library (its chunk and order rules follow the environment)
+    dev = qd.CudaDevice(0, timing=1, experiments=bool(os.environ.get("QVX_MEASURE_EXPERIMENTS")))
     rng = np.random.default_rng(7)
     if "c2" in names:
         attention_case(dev, "c2 attention: batch 64, ctx U[1024,4096], 32q/4kv, bf16, B16", wl.C2, rng.integers(1024, 4097, size=64))
