@@ -37,7 +37,6 @@ SOURCES = {
     "qvx_api.cu": [],
     "kv_rows.cu": [],
     "block_copy.cu": [],
-    "attn_split.cu": [],
     "attn_stream.cu": [],
     "attn_static.cu": [],
     "attn_exact.cu": ["-fmad=false", "-prec-div=true", "-prec-sqrt=true", "-ftz=false"],

@@ -92,6 +92,22 @@ __device__ __forceinline__ void fence_barrier_init() {
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// Plain shared-memory accesses by 32-bit shared address (a pointer kept in a struct loses its address space and
+// turns into generic loads, which wait on the long scoreboard).  Volatile: kept in order with the barrier waits.
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds64(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts64(uint32_t addr, float2 v) {
+    asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -293,30 +309,9 @@ __device__ __forceinline__ void merge_chunks_in_order(const float* p0, uint32_t 
     }
 }
 
-// ---- kernel arguments --------------------------------------------------------------------
-struct SplitArgs {
-    const uint8_t* pool;
-    const float* q;             // [token][head][d]
-    float* out;                 // [token][head][d]
-    float* partials;            // n_parts x (8*d + 16): acc[8][d], m[8], l[8]
-    uint32_t* counters;         // one per split (sequence, group): arrivals so far; zero between launches
-    const uint32_t* items;      // n_items x item_words: header, then the item's block ids
-    int* status;                // a kernel that gave up a wait leaves a code here
-    uint64_t block_bytes;
-    uint32_t page_bytes, row_bytes, tiles_per_block, heads, d, item_words;
-    float scale_log2;           // (1 / sqrt(d)) * log2(e)
-};
-
+// ---- a work item's header -----------------------------------------------------------------
 struct Item {
     uint32_t seq, tokens, head0, nheads, kv_head, part, part0, nch, counter;
 };
-__device__ __forceinline__ Item load_item(const uint32_t* w) {
-    uint4 a = *reinterpret_cast<const uint4*>(w), b = *reinterpret_cast<const uint4*>(w + 4);
-    Item it;
-    it.seq = a.x; it.tokens = a.y; it.head0 = a.z; it.nheads = a.w & 0xffffu; it.kv_head = a.w >> 16;
-    it.part = b.x; it.part0 = b.y; it.nch = b.z; it.counter = b.w;
-    return it;
-}
-
 
 }  // namespace qvx

@@ -1,4 +1,5 @@
-// Paged decode attention over 16-bit pools: a persistent, warp-specialised streaming kernel.
+// Paged decode attention over native-layout pools (bf16, f16 on the tensor cores; f32 on the CUDA cores): a
+// persistent, warp-specialised streaming kernel.
 //
 // Computes what `attn_decode.comp` (crates/qubivex-backend-vulkan/shaders/attn_decode.comp:60-175)
 // and the gather + `attend` of the CPU device (crates/qubivex-backend-cpu/src/sim.rs:400-429,
@@ -24,7 +25,8 @@
 //     with its own online-softmax state: S^T = K Q^T for the tile (16 positions x 8 heads,
 //     m16n8k16 with K as the A operand straight from the swizzled page), then
 //     O^T += V^T P^T (V through ldmatrix.trans, P transposed in registers by movmatrix).
-//     Every key and value byte is read from shared memory exactly once.
+//     Every key and value byte is read from shared memory exactly once.  (f32 pools: the same warps, the same
+//     tiles and states, the products on the CUDA cores, two per instruction; see WarpState32.)
 //   - The consumer warps never wait for one another.  At the end of a chunk each leaves its state
 //     (maxima, row sums, unnormalised outputs over the tiles it took) in one of two buffers in
 //     shared memory, arrives on the buffer's mbarrier and goes on with the next chunk's tiles.
@@ -138,11 +140,12 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int D>
+// E: bytes per pool element (2: bf16 / f16, 4: f32).
+template <int D, int E = 2>
 struct StreamSmem {
     static constexpr int ctas_per_sm = (D <= 128 && CW <= 4) ? 2 : 1;
     static constexpr uint32_t budget = (227u * 1024u) / ctas_per_sm - 1024u;
-    static constexpr uint32_t tile_bytes = TILE * D * 2;
+    static constexpr uint32_t tile_bytes = TILE * D * E;
     static constexpr uint32_t stage_bytes = 2 * tile_bytes;
     static constexpr uint32_t q_stride = D * 4 + 16;  // padded rows: fragment reads hit 32 distinct banks
     // One warp's state: m[8], l[8], acc[8][D] with rows of D + 4 floats: the lanes that hold heads 2t
@@ -152,7 +155,11 @@ struct StreamSmem {
     static constexpr uint32_t res_bytes = MAIL_SLOTS * CW * res_floats * 4;  // two items' worth: one being merged, one being filled
     static constexpr uint32_t q_bytes = Q_SLOTS * 8 * q_stride;
     static constexpr uint32_t rec_bytes = REC_SLOTS * REC_WORDS * 4;
-    static constexpr uint32_t fixed = res_bytes + q_bytes + rec_bytes + 1024;
+    // f32 pools: the consumers' probabilities of a tile, [position][8 heads] of (p, p) pairs per warp
+    static constexpr uint32_t ps_bytes = E == 4 ? CW * TILE * 8 * 8 : 0;
+    // (+ the barriers, the notes and the last word; an f32 ring has at most 8 stages, and d = 128 only fits its four
+    // 16 KB stages beside a second CTA with the smaller allowance)
+    static constexpr uint32_t fixed = res_bytes + q_bytes + rec_bytes + ps_bytes + (E == 4 ? 512 : 1024);
     static constexpr uint32_t stages_fit = (budget - fixed) / stage_bytes;
     // A multiple of CW: tile n goes to stage n % stages and to warp n % CW, so a stage is
     // always read by the same warp and a warp waits for its stages' phases strictly in order
@@ -166,13 +173,15 @@ struct StreamSmem {
     static constexpr uint32_t res_off = stages * stage_bytes;
     static constexpr uint32_t q_off = res_off + res_bytes;
     static constexpr uint32_t rec_off = q_off + q_bytes;
-    static constexpr uint32_t bar_off = rec_off + rec_bytes;
+    static constexpr uint32_t ps_off = rec_off + rec_bytes;
+    static constexpr uint32_t bar_off = ps_off + ps_bytes;
     // full[stages], empty[stages], qfull[Q_SLOTS], qempty[Q_SLOTS], rec[REC_SLOTS],
     // res_full[MAIL_SLOTS], res_free[MAIL_SLOTS], note[NOTE_SLOTS], then the notes
     static constexpr uint32_t n_bars = 2 * stages + 2 * Q_SLOTS + REC_SLOTS + 2 * MAIL_SLOTS + NOTE_SLOTS;
     static constexpr uint32_t mail_off = (bar_off + n_bars * 8 + 15u) & ~15u;
     static constexpr uint32_t final_off = mail_off + NOTE_SLOTS * 32;  // chunks this CTA hands over in all, once its producer knows
     static constexpr uint32_t total = final_off + 16;
+    static_assert(total <= budget, "the CTA's shared memory fits beside its neighbour's");
 #if QVX_CW <= 4  // (experiment builds with more consumer warps only run the head sizes that fit)
     static_assert(stages >= CW, "the ring needs a stage per consumer warp");
 #endif
@@ -484,9 +493,244 @@ __device__ __forceinline__ void climb(const StreamArgs& a, const Mail& it, uint3
     }
 }
 
-template <int DT, int D, int PRECISE>
-__global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) attn_stream_kernel(StreamArgs a) {
-    using SM = StreamSmem<D>;
+// ---- what a consumer warp carries through a chunk ---------------------------------------------------------
+// Two forms with one interface: begin_item (the group's queries), begin_chunk, tile, store (the warp's state into
+// the hand-over buffer: m[8], l[8], then acc[8][res_row]).  `queries_in_registers`: the query slot is free as soon
+// as begin_item returns; otherwise the warp reads it until the item's last tile.
+template <int DT, int D, int PASSES>
+struct WarpState16 {   // bf16 / f16 pools: tensor cores (attend_tile)
+    static constexpr bool queries_in_registers = true;
+    uint32_t qf[D / 16][2], ql[D / 16][2];
+    float o[D / 16][4];
+    float m0, m1, l0, l1;  // heads 2t and 2t+1
+    __device__ __forceinline__ void begin_item(const uint8_t* qslot, uint32_t q_stride, uint32_t nheads, uint32_t lane, uint8_t*) {
+        // Q^T fragments (the B operand), once per item: this lane holds head g, dims 16*ks + 2t + {0,1,8,9}.
+        const uint32_t g = lane >> 2, t = lane & 3;
+        const bool live = g < nheads;
+        const float* qrow = reinterpret_cast<const float*>(qslot + g * q_stride);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ks++) {
+            float2 x0 = make_float2(0.f, 0.f), x1 = x0;
+            if (live) {
+                x0 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t);
+                x1 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t + 8);
+            }
+            split16<DT>(x0.x, x0.y, qf[ks][0], ql[ks][0]);
+            split16<DT>(x1.x, x1.y, qf[ks][1], ql[ks][1]);
+        }
+    }
+    __device__ __forceinline__ void begin_chunk() {
+#pragma unroll
+        for (int m = 0; m < D / 16; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; }
+        m0 = m1 = -INFINITY; l0 = l1 = 0.f;
+    }
+    __device__ __forceinline__ void tile(uint32_t kt, uint32_t vt, uint8_t*, uint8_t* vt_rows, uint32_t valid, uint32_t lane, float scale_log2) {
+        attend_tile<DT, D, PASSES>(kt, vt, vt_rows, valid, lane, qf, ql, scale_log2, o, m0, m1, l0, l1);
+    }
+    __device__ __forceinline__ void store(float* res, uint32_t res_row, uint32_t lane) {
+        const uint32_t g = lane >> 2, t = lane & 3;
+        // Row sums over the positions held by the other lanes of the same t.
+#pragma unroll
+        for (int sh = 4; sh <= 16; sh <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+        }
+        if (g == 0) {
+            res[2 * t] = m0; res[2 * t + 1] = m1;
+            res[8 + 2 * t] = l0; res[8 + 2 * t + 1] = l1;
+        }
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+            res[16 + (2 * t) * res_row + 16 * mt + g] = o[mt][0];
+            res[16 + (2 * t + 1) * res_row + 16 * mt + g] = o[mt][1];
+            res[16 + (2 * t) * res_row + 16 * mt + g + 8] = o[mt][2];
+            res[16 + (2 * t + 1) * res_row + 16 * mt + g + 8] = o[mt][3];
+        }
+    }
+};
+
+// f32 pools: CUDA cores.  Scores: lane = (position = lane & 15, half = lane >> 4) computes heads half, half + 2, ...
+// of the group's NH; values: lane owns output dims 2 lane, 2 lane + 1 (+ 64) of all NH heads.  The multiply-adds go
+// out two at a time (fma.rn.f32x2): a score is summed as an even and an odd half.  The queries stay in their shared-
+// memory slot for the whole item; `ps` holds the tile's probabilities as (p, p) pairs between the two phases.
+// Every pair lives in one 64-bit register from its load to its last use (P2): taken apart and put together again
+// around each instruction, a pair costs two moves per multiply-add.
+using P2 = unsigned long long;
+__device__ __forceinline__ P2 fma2(P2 a, P2 b, P2 c) {
+    P2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ P2 mul2(P2 a, P2 b) {
+    P2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ P2 pair_of(float x, float y) {
+    P2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(x), "f"(y));
+    return d;
+}
+__device__ __forceinline__ float2 floats_of(P2 p) {
+    float2 v;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(v.x), "=f"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void lds_pairs(uint32_t addr, P2& a, P2& b) {   // 16 bytes: two pairs
+    asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
+}
+__device__ __forceinline__ P2 lds_pair(uint32_t addr) {
+    P2 a;
+    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(a) : "r"(addr));
+    return a;
+}
+__device__ __forceinline__ void sts_pair(uint32_t addr, P2 v) { asm volatile("st.shared.b64 [%0], %1;" ::"r"(addr), "l"(v) : "memory"); }
+
+template <int D, int NH>
+struct WarpState32 {
+    static constexpr bool queries_in_registers = false;
+    static constexpr int NJ = NH / 2, DK = D / 64;
+    uint32_t q;         // shared address of [8] rows of q_stride bytes; rows past the group's heads hold anything
+    uint32_t q_stride, nheads;
+    uint32_t ps;        // shared address of this warp's [16 positions][8 heads] (p, p) pairs
+    float m[NH], lpart[NJ];
+    P2 o[NH][DK];
+    __device__ __forceinline__ void begin_item(const uint8_t* qslot, uint32_t stride, uint32_t nh, uint32_t, uint8_t* ps_warp) {
+        q = smem_u32(qslot); q_stride = stride; nheads = nh;
+        ps = smem_u32(ps_warp);
+    }
+    __device__ __forceinline__ void begin_chunk() {
+#pragma unroll
+        for (int h = 0; h < NH; h++) {
+            m[h] = -INFINITY;
+#pragma unroll
+            for (int k = 0; k < DK; k++) o[h][k] = 0ull;   // (0.f, 0.f)
+        }
+#pragma unroll
+        for (int j = 0; j < NJ; j++) lpart[j] = 0.f;
+    }
+    __device__ __forceinline__ void tile(uint32_t kt, uint32_t vt, uint8_t*, uint8_t*, uint32_t valid, uint32_t lane, float scale_log2) {
+        const uint32_t tok = lane & 15, half = lane >> 4;
+        P2 s2[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) s2[j] = 0ull;
+        const uint32_t krow = kt + tok * (D * 4), qrow = q + half * q_stride, sw = (tok & 7) << 4;
+#pragma unroll 8
+        for (int c = 0; c < D / 4; c++) {
+            P2 k01, k23;
+            lds_pairs(krow + ((c << 4) ^ sw), k01, k23);
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                P2 q01, q23;
+                lds_pairs(qrow + 2 * j * q_stride + 16 * c, q01, q23);
+                s2[j] = fma2(q01, k01, s2[j]);
+                s2[j] = fma2(q23, k23, s2[j]);
+            }
+        }
+        float s[NJ];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            // (a head past the group's: its query row is whatever the slot held; its scores are made harmless)
+            const float2 two = floats_of(s2[j]);
+            s[j] = (half + 2 * j < nheads && tok < valid) ? (two.x + two.y) * scale_log2 : -INFINITY;
+        }
+        // Tile maximum per head over the 16 positions, then across the two halves.
+        float mx[NH];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            float v = s[j];
+#pragma unroll
+            for (int sh = 1; sh <= 8; sh <<= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, sh));
+            const float other = __shfl_xor_sync(0xffffffffu, v, 16);
+            mx[2 * j] = half == 0 ? v : other;       // head half + 2j is mine, head (1 - half) + 2j the other half's
+            mx[2 * j + 1] = half == 0 ? other : v;
+        }
+        float al[NH];
+        bool moved = false;
+#pragma unroll
+        for (int h = 0; h < NH; h++) {
+            const float mn = fmaxf(m[h], mx[h]);
+            // (a head with no valid score yet keeps -inf; exp2(-inf - -inf) would be NaN)
+            al[h] = mn == -INFINITY ? 1.0f : ex2(m[h] - mn);
+            moved = moved || al[h] != 1.0f;
+            m[h] = mn;
+        }
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const float mine = half == 0 ? m[2 * j] : m[2 * j + 1];
+            const float al_mine = half == 0 ? al[2 * j] : al[2 * j + 1];
+            const float pr = s[j] == -INFINITY ? 0.0f : ex2(s[j] - mine);
+            lpart[j] = fmaf(lpart[j], al_mine, pr);
+            sts_pair(ps + (tok * 8 + half + 2 * j) * 8, pair_of(pr, pr));
+        }
+        __syncwarp();
+        if (moved) {   // (the maxima settle after a chunk's first tiles: x * 1.0f is x, so skipping changes no bit)
+#pragma unroll
+            for (int h = 0; h < NH; h++) {
+                const P2 a2 = pair_of(al[h], al[h]);
+#pragma unroll
+                for (int k = 0; k < DK; k++) o[h][k] = mul2(o[h][k], a2);
+            }
+        }
+        // This lane's dims 2 lane, 2 lane + 1 (+ 64 k) of a value row: one 8-byte load in the row's swizzled chunk.
+        const uint32_t vlane = lane << 3;   // byte offset of the pair in an unswizzled row: chunk lane >> 1, half lane & 1
+        auto accumulate = [&](uint32_t p) {
+            P2 pv[NH];
+#pragma unroll
+            for (int h = 0; h < NH; h += 2) lds_pairs(ps + (p * 8 + h) * 8, pv[h], pv[h + 1]);
+#pragma unroll
+            for (int k = 0; k < DK; k++) {
+                // (chunk (lane >> 1) + 16 k of the row, swizzled by the row's place; the lane's half of the chunk)
+                const P2 v = lds_pair(vt + p * (D * 4) + 256u * k + (vlane ^ ((p & 7) << 4)));
+#pragma unroll
+                for (int h = 0; h < NH; h++) o[h][k] = fma2(pv[h], v, o[h][k]);
+            }
+        };
+        if (valid == TILE) {
+#pragma unroll
+            for (uint32_t p = 0; p < TILE; p++) accumulate(p);
+        } else {
+            for (uint32_t p = 0; p < valid; p++) accumulate(p);   // (rows past `valid` may hold anything, NaNs included)
+        }
+        __syncwarp();  // the probabilities are read: the next tile may overwrite them
+    }
+    __device__ __forceinline__ void store(float* res, uint32_t res_row, uint32_t lane) {
+        const uint32_t half = lane >> 4;
+        // Row sums: over the 16 positions, then hand each half's heads to the other.
+        float l[NH];
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            float v = lpart[j];
+#pragma unroll
+            for (int sh = 1; sh <= 8; sh <<= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
+            const float other = __shfl_xor_sync(0xffffffffu, v, 16);
+            l[2 * j] = half == 0 ? v : other;
+            l[2 * j + 1] = half == 0 ? other : v;
+        }
+        if (lane < 8) {   // heads past NH: no weight in any merge
+            float mv = -INFINITY, lv = 0.f;
+#pragma unroll
+            for (int h = 0; h < NH; h++)
+                if (lane == (uint32_t)h) { mv = m[h]; lv = l[h]; }
+            res[lane] = mv; res[8 + lane] = lv;
+        }
+#pragma unroll
+        for (int h = 0; h < NH; h++) {
+#pragma unroll
+            for (int k = 0; k < DK; k++) *reinterpret_cast<float2*>(res + 16 + h * res_row + 2 * lane + 64 * k) = floats_of(o[h][k]);
+        }
+    }
+};
+template <int DT, int D, int VAR> struct WarpStateOf { using type = WarpState16<DT, D, VAR>; };
+template <int D, int VAR> struct WarpStateOf<QVX_F32, D, VAR> { using type = WarpState32<D, VAR>; };
+
+// VAR: for bf16 / f16 pools, which operands go through the tensor cores as value + remainder (bit 0: the queries,
+// bit 1: the probabilities); for f32 pools, the query heads of a group the arithmetic is unrolled for (2, 4 or 8).
+template <int DT, int D, int VAR>
+__global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D, (DT == QVX_F32 ? 4 : 2)>::ctas_per_sm) attn_stream_kernel(StreamArgs a) {
+    constexpr int E = DT == QVX_F32 ? 4 : 2;
+    using SM = StreamSmem<D, E>;
+    using WS = typename WarpStateOf<DT, D, VAR>::type;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t sbase = smem_u32(smem);
@@ -632,17 +876,21 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 if (last_chunk) {
                     const uint32_t p = tokens - 1, B = a.tiles_per_block * TILE, slot = p % B;
                     const uint32_t blk = rec[QVX_ITEM_HEADER_WORDS + p / B];
-                    uint8_t* row = const_cast<uint8_t*>(base) + (uint64_t)blk * a.block_bytes + (uint64_t)slot * (D * 2);
-                    constexpr uint32_t CPR = D * 2 / 16;  // 16-byte chunks per row
+                    uint8_t* row = const_cast<uint8_t*>(base) + (uint64_t)blk * a.block_bytes + (uint64_t)slot * (D * E);
+                    constexpr uint32_t CPR = D * E / 16;  // 16-byte chunks per row
                     for (uint32_t i = lane; i < 2 * CPR; i += 32) {
                         const uint32_t kv = i / CPR, c = i % CPR;
-                        const float* src = (kv ? a.v_new : a.k_new) + (size_t)seq * a.kv_out + kvh * D + c * 8;
-                        const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+                        const float* src = (kv ? a.v_new : a.k_new) + (size_t)seq * a.kv_out + kvh * D + c * (16 / E);
                         uint4 w;
-                        w.x = narrow16x2(lo.x, lo.y, DT);
-                        w.y = narrow16x2(lo.z, lo.w, DT);
-                        w.z = narrow16x2(hi.x, hi.y, DT);
-                        w.w = narrow16x2(hi.z, hi.w, DT);
+                        if constexpr (E == 4) {
+                            w = *reinterpret_cast<const uint4*>(src);
+                        } else {
+                            const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+                            w.x = narrow16x2(lo.x, lo.y, DT);
+                            w.y = narrow16x2(lo.z, lo.w, DT);
+                            w.z = narrow16x2(hi.x, hi.y, DT);
+                            w.w = narrow16x2(hi.z, hi.w, DT);
+                        }
                         *reinterpret_cast<uint4*>(row + (uint64_t)kv * a.page_bytes + ((c ^ (slot & 7u)) << 4)) = w;
                     }
                     __threadfence();  // the rows are in device memory ...
@@ -808,8 +1056,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
     }
 
     // ================================ consumers ================================
-    const uint32_t g = lane >> 2, t = lane & 3;
     float* res_all = reinterpret_cast<float*>(smem + SM::res_off);
+    WS ws;
     uint32_t nbase = 0;   // tiles of the items before this one
     Tracer tr(a.trace_id, warp == 0 ? 2 : 3, lane == 0 && (warp == 0 || warp == CW - 1));
     bool dead = false;    // this warp gave up a wait
@@ -848,23 +1096,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             return;
         }
         tr.mark(20);  // item header read
-        // Q^T fragments (the B operand), once per item: this lane holds head g, dims 16*ks + 2t + {0,1,8,9}.
-        uint32_t qf[D / 16][2], ql[D / 16][2];
-        {
-            {
-                const bool live = g < it.nheads;
-                const float* qrow = reinterpret_cast<const float*>(smem + SM::q_off + (qslot * 8 + g) * SM::q_stride);
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ks++) {
-                    float2 x0 = make_float2(0.f, 0.f), x1 = x0;
-                    if (live) {
-                        x0 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t);
-                        x1 = *reinterpret_cast<const float2*>(qrow + 16 * ks + 2 * t + 8);
-                    }
-                    split16<DT>(x0.x, x0.y, qf[ks][0], ql[ks][0]);
-                    split16<DT>(x1.x, x1.y, qf[ks][1], ql[ks][1]);
-                }
-            }
+        ws.begin_item(smem + SM::q_off + qslot * 8 * SM::q_stride, SM::q_stride, it.nheads, lane, smem + SM::ps_off + warp * (TILE * 8 * 8));
+        if (WS::queries_in_registers) {
             __syncwarp();
             if (lane == 0) mbar_arrive(qempty0 + qslot * 8);  // the producer may reuse this query slot
         }
@@ -887,10 +1120,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
         // the merge runs in the order of the tiles' places in the chunk and the sum order does not
         // depend on how many tiles this CTA happened to stream before it.
         const uint32_t first = (warp + CW - nbase % CW) % CW;
-        float o[D / 16][4];
-#pragma unroll
-        for (int m = 0; m < D / 16; m++) { o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.f; }
-        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // heads 2t and 2t+1
+        ws.begin_chunk();
         {
             const uint32_t ntiles = (ctokens + TILE - 1) / TILE;
             for (uint32_t tau = first; tau < ntiles; tau += CW) {
@@ -900,8 +1130,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
                 const uint32_t kt = sbase + SM::ring_off + st * SM::stage_bytes, vt = kt + SM::tile_bytes;
                 const uint32_t valid = min((uint32_t)TILE, ctokens - tau * TILE);
 #if !(defined(QVX_EXPERIMENTS) && defined(QVX_EXPERIMENT_NOCOMPUTE))
-                attend_tile<DT, D, PRECISE>(kt, vt, smem + SM::ring_off + st * SM::stage_bytes + SM::tile_bytes, valid, lane, qf, ql,
-                                            a.scale_log2, o, m0, m1, l0, l1);
+                ws.tile(kt, vt, smem + SM::ring_off + st * SM::stage_bytes, smem + SM::ring_off + st * SM::stage_bytes + SM::tile_bytes, valid,
+                        lane, a.scale_log2);
 #else
                 (void)kt; (void)vt; (void)valid;
 #endif
@@ -911,12 +1141,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             nbase += ntiles;
         }
         tr.mark(21);  // tiles done
-        // Row sums over the positions held by the other lanes of the same t.
-#pragma unroll
-        for (int sh = 4; sh <= 16; sh <<= 1) {
-            l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
-        }
         if (dead) {
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
@@ -927,55 +1151,53 @@ __global__ void __launch_bounds__(STREAM_THREADS, StreamSmem<D>::ctas_per_sm) at
             if (lane == 0) atomicExch(a.status, STATUS_WAIT_TIMEOUT);
             return;
         }
-        float* res = res_all + (ms * CW + first) * SM::res_floats;
-        if (g == 0) {
-            res[2 * t] = m0; res[2 * t + 1] = m1;
-            res[8 + 2 * t] = l0; res[8 + 2 * t + 1] = l1;
-        }
-#pragma unroll
-        for (int mt = 0; mt < D / 16; mt++) {
-            res[16 + (2 * t) * SM::res_row + 16 * mt + g] = o[mt][0];
-            res[16 + (2 * t + 1) * SM::res_row + 16 * mt + g] = o[mt][1];
-            res[16 + (2 * t) * SM::res_row + 16 * mt + g + 8] = o[mt][2];
-            res[16 + (2 * t + 1) * SM::res_row + 16 * mt + g + 8] = o[mt][3];
-        }
+        ws.store(res_all + (ms * CW + first) * SM::res_floats, SM::res_row, lane);
         __syncwarp();
         if (lane == 0) mbar_arrive(rfull0 + ms * 8);
         tr.mark(23);  // state handed over
         }  // chunks of the item
+        if (!WS::queries_in_registers && lane == 0) mbar_arrive(qempty0 + qslot * 8);  // (the __syncwarp above: every lane is done with the queries)
     }
 }
 
 // ---- host side -----------------------------------------------------------------------------------
 extern int* device_status_word(qvx_device* dev);
 
-bool attn_stream_supported(const Layout& L, size_t heads) {
-    if (L.layout != QVX_LAYOUT_NATIVE || L.dtype == QVX_F32) return false;
-    if (L.B % TILE != 0 || heads % L.kvh != 0) return false;
+// The geometries this kernel serves: native-layout pools of any dtype, blocks of whole tiles, GQA groups.
+// Everything else runs in the reference's operation order (attn_exact.cu).
+bool attn_split_supported(const Layout& L, size_t heads) {
+    if (L.layout != QVX_LAYOUT_NATIVE) return false;
+    if (L.B % TILE != 0 || heads == 0 || heads % L.kvh != 0) return false;
+    if (L.dtype == QVX_F32) return L.d == 64 || L.d == 128;
     return L.d == 64 || L.d == 128 || L.d == 256;
 }
+// The new position's rows are stored by the attention launch itself.
+bool attn_split_fuses_append(const Layout& L, size_t heads) { return attn_split_supported(L, heads); }
 
-// Floats of scratch one partial result takes; partial slots and arrival counters a split
-// (sequence, group) of `nch` chunks takes (the merge tree's entries and nodes).
-size_t attn_stream_partial_floats(uint32_t d) { return 8 * (size_t)d + 16; }
-uint32_t attn_stream_parts(uint32_t nch) { return merge_entries_total(nch); }
-uint32_t attn_stream_counters(uint32_t nch) { return merge_counters_total(nch); }
+// Floats of scratch the partial results take; partial slots and arrival counters a split (sequence, group) of
+// `nch` chunks takes (the merge tree's entries and nodes).
+size_t attn_partial_floats(const qvx_tables* t) { return t->n_parts * (8 * (size_t)t->L.d + 16); }
+uint32_t attn_parts_per_group(const Layout&, uint32_t nch) { return merge_entries_total(nch); }
+uint32_t attn_counters_per_group(const Layout&, uint32_t nch) { return merge_counters_total(nch); }
 
-template <int DT, int D, int PRECISE>
+template <int DT, int D, int VAR>
 static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t s) {
-    auto kernel = attn_stream_kernel<DT, D, PRECISE>;
+    using SM = StreamSmem<D, (DT == QVX_F32 ? 4 : 2)>;
+    // (the cross-chunk merge stages a node's entries in the ring, sized by the 16-bit layout's)
+    static_assert(SM::stages * SM::stage_bytes >= MERGE_FAN * (8 * D + 16) * 4 || D > 128, "the ring holds a merge node's entries");
+    auto kernel = attn_stream_kernel<DT, D, VAR>;
     static int per_device[64] = {};  // set up once per device (the attribute belongs to the device's context)
     int& ctas_per_sm = per_device[dev->ordinal & 63];
     if (!ctas_per_sm) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)StreamSmem<D>::total);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::total);
         if (e == cudaSuccess)
-            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kernel, STREAM_THREADS, StreamSmem<D>::total);
+            e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kernel, STREAM_THREADS, SM::total);
         if (e != cudaSuccess) { ctas_per_sm = 0; return check_cuda(dev, e, "streaming attention set-up"); }
         if (ctas_per_sm < 1) ctas_per_sm = 1;
     }
     const unsigned grid = (unsigned)std::min<size_t>(a.n_items, (size_t)ctas_per_sm * dev->prop.multiProcessorCount);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(STREAM_THREADS); cfg.dynamicSmemBytes = StreamSmem<D>::total; cfg.stream = s;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(STREAM_THREADS); cfg.dynamicSmemBytes = SM::total; cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -1002,9 +1224,9 @@ static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t 
     return check_cuda(dev, cudaLaunchKernelEx(&cfg, kernel, a), "streaming attention launch");
 }
 
-int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
-                           float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
-                           bool overlap, cudaStream_t s) {
+int32_t launch_attn_split(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
+                          float* partials, uint32_t* counters, uint32_t* queue, const float* k_new, const float* v_new,
+                          bool overlap, cudaStream_t s) {
     if (t->n_items == 0) return QVX_OK;
     const Layout& L = t->L;
     if (t->item_words > REC_WORDS)
@@ -1049,6 +1271,13 @@ int32_t launch_attn_stream(qvx_device* dev, qvx_tables* t, const void* pool, con
     }
 #endif
     QVX_STREAM_CASE(QVX_F16, 64, 0) QVX_STREAM_CASE(QVX_F16, 128, 0) QVX_STREAM_CASE(QVX_F16, 256, 0)
+    if (L.dtype == QVX_F32) {
+        // The arithmetic is unrolled over the query heads of a group (items hold up to 8 of them).
+        const size_t group = t->heads / L.kvh;
+        passes = group <= 2 ? 2 : group <= 4 ? 4 : 8;
+        QVX_STREAM_CASE(QVX_F32, 64, 2) QVX_STREAM_CASE(QVX_F32, 64, 4) QVX_STREAM_CASE(QVX_F32, 64, 8)
+        QVX_STREAM_CASE(QVX_F32, 128, 2) QVX_STREAM_CASE(QVX_F32, 128, 4) QVX_STREAM_CASE(QVX_F32, 128, 8)
+    }
 #undef QVX_STREAM_CASE
     if (rc == QVX_ERR_UNSUPPORTED) return fail(dev, rc, "streaming attention: no kernel for this geometry");
     return rc;

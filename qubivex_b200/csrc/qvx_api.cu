@@ -412,7 +412,7 @@ static QueueOrder queue_order() {
 // CTAs of the streaming attention kernel the device keeps resident for this geometry; 0 when another
 // kernel serves it (one CTA per item there: items stay single chunks).
 static uint32_t stream_ctas(const qvx_device* dev, const Layout& L, size_t heads) {
-    if (L.dtype == QVX_F32 || !attn_split_supported(L, heads)) return 0;
+    if (!attn_split_supported(L, heads)) return 0;
     return (uint32_t)dev->prop.multiProcessorCount * (L.d <= 128 ? 2u : 1u);
 }
 

@@ -54,6 +54,8 @@ def _report(name, byts, sec):
 
 
 def attention_case(dev, name, shape: wl.Shape, lengths, shared_prefix=0, sharers=0, variant=qd.ATTN_SPLIT, dtype=qd.BF16, seed=1):
+    import dataclasses
+    shape = dataclasses.replace(shape, dtype={qd.F32: "f32", qd.BF16: "bf16", qd.F16: "f16"}[dtype])  # (the bytes follow the pool's type)
     geo = qd.geometry(shape.block_tokens, shape.kv_heads, shape.head_dim, dtype, qd.LAYOUT_NATIVE)
     bb = qd.block_bytes(geo)
     B = shape.block_tokens
@@ -196,6 +198,8 @@ def main(names):
     if "f32" in names:
         big = wl.Shape("f32-big", 8, 2, 64, 16, "f32", 64, 1024, 4096)
         attention_case(dev, "split f32 at size: batch 64, ctx U[1024,4096], 8q/2kv d64", big, rng.integers(1024, 4097, size=64), dtype=qd.F32)
+    if "f32c2" in names:
+        attention_case(dev, "split f32, c2's shape: batch 64, ctx U[1024,4096], 32q/4kv d128", wl.C2, np.random.default_rng(7).integers(1024, 4097, size=64), dtype=qd.F32)
     if "copy" in names:
         copy_case(dev, "block copy: 1474 moves of 128 KiB in a 16384-block pool", wl.C4, 16384, 1474)
     if "prelude" in names:

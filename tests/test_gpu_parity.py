@@ -254,9 +254,12 @@ def test_kernel_times_are_counted(dev):
     kt = dev.kernel_times()
     c32 = Case(8, 2, 64, 16, "f32", [600, 100], seed=82)
     c32.run_device(dev, variant=qd.ATTN_SPLIT)
-    assert dev.kernel_times()["append"][0] == 1   # f32 pool: its own launch
+    assert dev.kernel_times()["append"][0] == 0   # f32 native pool: the same kernel, the same fused append
+    cref = Case(8, 2, 64, 16, "f32", [600, 100], seed=82, layout=qd.LAYOUT_REFERENCE)
+    cref.run_device(dev)
+    assert dev.kernel_times()["append"][0] == 1   # a pool in the reference's layout: the append is its own launch
     assert kt["sync"][0] == 1 and kt["attn"][0] == 1
-    assert kt["append"][0] == 0   # 16-bit native pool: the append rides in the attention launch
+    assert kt["append"][0] == 0   # native pool: the append rides in the attention launch
     assert kt["attn"][1] > 0
     t = dev.transfers()
     assert t.submissions >= 1 and t.activations_out >= c.q.nbytes and t.timed >= 2
