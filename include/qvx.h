@@ -193,7 +193,7 @@ int32_t qvx_attn_decode(qvx_device *dev, qvx_tables *tables, const void *pool, c
 
 /* The two stages of a decode step in the reference's order — each token's new row stored at
  * pos[t], then attention over 0..=pos[t] (crates/qubivex-backend-cpu/src/sim.rs:394-429;
- * `attn_prelude.comp` then `attn_decode.comp`) — as one call.  On 16-bit native pools the rows are
+ * `attn_prelude.comp` then `attn_decode.comp`) — as one call.  On native-layout pools the rows are
  * stored inside the attention launch (by the CTA that reads them); otherwise this is
  * qvx_kv_append followed by qvx_attn_decode.  k_new, v_new: s x kv_out f32. */
 int32_t qvx_kv_append_attn_decode(qvx_device *dev, qvx_tables *tables, void *pool, const float *k_new,

@@ -606,7 +606,7 @@ static int32_t ensure_partials(qvx_device* dev, size_t floats, size_t counters) 
 }
 
 // Attention, with the step's KV append in front of it when k_new / v_new are given: inside the
-// same launch where the kernel can (16-bit native pools), as its own launch otherwise.
+// same launch where the kernel can (native-layout pools), as its own launch otherwise.
 static int32_t run_attention(qvx_device* dev, qvx_tables* t, const void* pool, const float* q, float* out,
                              uint32_t variant_flags, cudaStream_t s, const float* k_new = nullptr, const float* v_new = nullptr) {
     const uint32_t variant = variant_flags & 0xffu;
