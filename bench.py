@@ -64,6 +64,33 @@ def env_int(name: str, default: int) -> int:
     return int(os.environ.get(name, default))
 
 
+def bind_near_gpu(local_rank: int) -> str:
+    """One process per GPU: keeps this process's threads -- and with them the pinned host buffers it is about
+    to allocate and touch -- on the cores next to its GPU (the affinity NVML reports for the device, within
+    what the process is allowed), so that eight ranks' host copies do not cross between sockets.  Changes nothing
+    of the GPU; returns what was done, for the JSON line."""
+    try:
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        try:
+            pr = torch.cuda.get_device_properties(local_rank)
+            bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        allowed = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (max(allowed) + 64) // 64)
+        near = {64 * w + b for w, bits in enumerate(words) for b in range(64) if (int(bits) >> b) & 1}
+        mine = near & allowed
+        if not mine or mine == allowed:
+            return f"unchanged ({len(allowed)} cores allowed, {len(near)} next to the GPU)"
+        os.sched_setaffinity(0, mine)
+        return f"{len(mine)} of {len(allowed)} allowed cores: those next to the GPU"
+    except Exception as e:  # no NVML, an old torch, a restricted container: the run goes on unbound
+        return f"unchanged ({type(e).__name__})"
+
+
 def config_of(shape: "wl.Shape", layers: int) -> dict:
     """The workload's description: the same keys and values in both arms."""
     return {"workload": shape.name, "layers": layers, "batch_per_gpu": shape.batch, "heads": shape.heads,
@@ -222,7 +249,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
 
     torch.cuda.set_device(local_rank)
     dist = None
+    host_cores = "unchanged (one process)"
     if world > 1:
+        host_cores = bind_near_gpu(local_rank)
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -402,7 +431,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     x1 = dev.transfers()
     ops = max(1, x1.submissions - x0.submissions)
     host_us = {"submit_us_per_op": (x1.submit_ns - x0.submit_ns) / ops / 1e3, "wait_us_per_op": (x1.wait_ns - x0.wait_ns) / ops / 1e3,
-               "what": "host time inside qvx_paged_attention_host per layer: queueing the copies and kernels, then waiting for the stream"}
+               "what": "host time inside qvx_paged_attention_host per layer: queueing the copies and kernels, then waiting for the stream",
+               "cores": host_cores}
     checksum = float(sum(float(o[0, 0, 0]) for o in oh))
     assert np.isfinite(checksum)
 
@@ -688,7 +718,7 @@ def run_c5(args, rank: int, local_rank: int, world: int) -> None:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": shape.name, "layers": 1, "batch": s, "heads": shape.heads, "kv_heads": shape.kv_heads, "head_dim": d,
                    "block_tokens": B, "context": [shape.ctx_lo, shape.ctx_hi],
-                   "partition": f"by KV head: {kvl} KV head(s) and {hl} query heads per GPU; one ncclAllGather of the outputs per step",
+                   "partition": f"by KV head: {kvl} KV head(s) and {hl} query heads per GPU; one exchange of the outputs per step (the gather object says which)",
                    "l2": f"each launch reads {algo_rank / 2**20:.0f} MiB of KV per GPU, once: no flush between iterations"},
         "roofline": {"bound": "hbm", "kernel": "attn_stream_kernel (paged decode attention), per GPU", "achieved": algo_rank / (attn_us * 1e-6) / 1e9,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": algo_rank / (attn_us * 1e-6) / 1e9 / peak,
