@@ -117,7 +117,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -457,6 +457,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                      "kernels_us_per_launch": {k: (v[1] / v[0] / 1e3 if v[0] else 0.0) for k, v in kt.items() if v[0]}},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "call": "qvx_paged_attention_host x layers per step: synchronous, one op per layer, as DiscreteDevice::routed_moe",
+                "d2h_how": "the outputs' host arrays are page-locked: the attention kernel stores into them over the bus while it runs (no copy out)",
                 "ms_each_step": each_ms, "host": host_us,
                 "pipelined": {"value": e2e_pipelined, "call": "qvx_paged_attention_host_async x layers + qvx_wait per step",
                               "ms_each_step": each_pipelined}},

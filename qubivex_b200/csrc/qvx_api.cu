@@ -954,6 +954,20 @@ static bool prelude_ok(const qvx_prelude* p) {
 
 // `pre` (host pointers), when given, runs the prelude on the staged q, k_new and v_new and copies
 // the new rows back into k_back / v_back.
+// The device's address for `bytes` of the caller's host array, or null when the device cannot reach it with plain
+// 16-byte stores: memory that is not page-locked, not mapped, or not 16-byte aligned.
+static float* mapped_host_pointer(const void* host, size_t bytes) {
+    if (!host || ((uintptr_t)host & 15u)) return nullptr;
+    cudaPointerAttributes at{}, end{};
+    if (cudaPointerGetAttributes(&at, host) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (at.type != cudaMemoryTypeHost || !at.devicePointer) return nullptr;
+    // (the whole range must be page-locked: look at its last byte as well)
+    if (cudaPointerGetAttributes(&end, (const char*)host + bytes - 1) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (end.type != cudaMemoryTypeHost || !end.devicePointer) return nullptr;
+    if ((const char*)end.devicePointer - (const char*)at.devicePointer != (ptrdiff_t)(bytes - 1)) return nullptr;
+    return (float*)at.devicePointer;
+}
+
 static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const qvx_geometry* geo, size_t heads,
                                       size_t s, const float* q, const float* k_new, const float* v_new,
                                       const uint32_t* pos, const uint32_t* blocks, size_t n_blocks,
@@ -1075,8 +1089,14 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     const float* d_sync = (const float*)(ds + o_sync);
     rc = launch_kv_rows(dev, L, pool->ptr, d_sync, d_sync + kv_out, 2 * kv_out, (const uint32_t*)(ds + o_syncto), nullptr,
                         nullptr, nullptr, n_sync, held, QVX_K_SYNC, cs);
+    // The outputs go straight into the caller's array when the device can address it (pinned memory, which
+    // unified addressing maps into the device's address space): the kernel's stores cross the bus while it runs,
+    // and the op needs no copy out.  Pageable (or misaligned) memory takes the staged copy.
+    float* d_out = s ? mapped_host_pointer(out, 4 * s * q_out) : nullptr;
+    const bool out_direct = d_out != nullptr;
+    if (!out_direct) d_out = (float*)(ds + o_out);
     if (rc == QVX_OK && s)
-        rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), (float*)(ds + o_out), variant, cs,
+        rc = run_attention(dev, t, pool->ptr, (const float*)(ds + o_q), d_out, variant, cs,
                            (const float*)(ds + o_k), (const float*)(ds + o_v));
     if (rc) return rc;
     if (!serial) {
@@ -1085,7 +1105,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
         cudaStreamWaitEvent(d2h, op.kernels_done, 0);
     }
     if (s) {
-        e = cudaMemcpyAsync(out, ds + o_out, 4 * s * q_out, cudaMemcpyDeviceToHost, d2h);
+        if (!out_direct) e = cudaMemcpyAsync(out, ds + o_out, 4 * s * q_out, cudaMemcpyDeviceToHost, d2h);
         if (e == cudaSuccess && k_back) e = cudaMemcpyAsync(k_back, ds + o_k, 4 * s * kv_out, cudaMemcpyDeviceToHost, d2h);
         if (e == cudaSuccess && v_back) e = cudaMemcpyAsync(v_back, ds + o_v, 4 * s * kv_out, cudaMemcpyDeviceToHost, d2h);
         if (e != cudaSuccess) return check_cuda(dev, e, "copy out");

@@ -371,6 +371,42 @@ def test_more_ops_in_flight_than_the_staging_ring_holds(dev):
         buf.free()
 
 
+@pytest.mark.parametrize("dtype,variant", [("bf16", qd.ATTN_SPLIT), ("f32", qd.ATTN_SPLIT), ("f32", qd.ATTN_EXACT)])
+def test_outputs_stored_straight_into_pinned_host_memory_have_the_staged_copys_bits(dev, dtype, variant):
+    """A page-locked, aligned `out` is written by the kernel itself over the bus; pageable or misaligned memory
+    takes the staged copy.  Same bits on every route, synchronous and queued, and right against the oracle."""
+    torch = pytest.importorskip("torch")
+    c = Case(8, 2, 64, 16, dtype, [1300, 37, 600, 16, 2049], seed=83)
+    _, want = c.run_oracle()
+    buf = dev.alloc(c.pool_blocks * c.bb)
+    try:
+        dev.write(buf, 0, c.host_pool())
+        call = lambda **kw: dev.paged_attention(buf, c.geo_d, c.heads, c.q, c.k_new, c.v_new, c.pos, c.blocks, c.table_at, c.sync,
+                                                c.sync_to, variant=variant, **kw)
+        staged = call()                                                        # numpy's pageable memory
+        shape = staged.shape
+        pinned = torch.full(shape, float("nan"), dtype=torch.float32).pin_memory()
+        call(out=pinned)
+        assert np.array_equal(pinned.numpy().view(np.uint32), staged.view(np.uint32))
+        queued = [torch.full(shape, float("nan"), dtype=torch.float32).pin_memory() for _ in range(3)]
+        for o in queued:
+            call(out=o, wait=False)
+        dev.wait()
+        for o in queued:
+            assert np.array_equal(o.numpy().view(np.uint32), staged.view(np.uint32))
+        # page-locked but 4 bytes off a 16-byte boundary: the staged route again
+        wide = torch.full((staged.size + 4,), float("nan"), dtype=torch.float32).pin_memory()
+        off = wide[1:1 + staged.size].view(shape)
+        assert off.data_ptr() % 16 != 0
+        call(out=off)
+        assert np.array_equal(off.numpy().view(np.uint32), staged.view(np.uint32))
+        assert torch.isnan(wide[0]) and bool(torch.isnan(wide[1 + staged.size:]).all())
+        ok, err = within(staged, want, dtype) if variant != qd.ATTN_EXACT else (np.array_equal(staged.view(np.uint32), want.view(np.uint32)), "bits")
+        assert ok, err
+    finally:
+        buf.free()
+
+
 def test_batch_invariance_when_ctas_stream_many_ragged_items(dev):
     # More (sequence, group) pairs than resident CTAs, lengths that are no multiple of anything:
     # every CTA streams several items, and most start at an arbitrary place of its tile stream.
