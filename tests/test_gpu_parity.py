@@ -108,6 +108,7 @@ def test_nan_and_inf_keys_follow_the_reference(dev):
 # ---- split attention: tolerance ---------------------------------------------------------------
 @pytest.mark.parametrize("dtype,heads,kvh,d,B", [
     ("f32", 8, 2, 64, 16), ("f32", 4, 4, 128, 16), ("f32", 16, 2, 64, 32), ("f32", 2, 1, 64, 16),
+    ("f32", 6, 2, 64, 16), ("f32", 10, 2, 128, 16), ("f32", 12, 1, 128, 32), ("f32", 7, 1, 64, 16),   # groups of 3, 5, 8 + 4, 7
     ("bf16", 32, 4, 128, 16), ("bf16", 32, 8, 128, 32), ("bf16", 8, 8, 64, 16), ("bf16", 24, 2, 128, 16),
     ("bf16", 8, 1, 256, 16), ("f16", 32, 4, 128, 16), ("f16", 4, 2, 64, 64), ("bf16", 64, 8, 128, 256),
 ])
@@ -122,16 +123,17 @@ def test_split_attention_is_within_tolerance(dev, dtype, heads, kvh, d, B):
     assert np.all(np.isfinite(got))
 
 
-def test_long_contexts_take_larger_chunks_and_a_merge_tree(dev):
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_long_contexts_take_larger_chunks_and_a_merge_tree(dev, dtype):
     # 20000 positions: 1024-position chunks; 40000 and 70000: 2048-position chunks, the last
     # with more than 32 of them (two levels of the fan-in-8 merge tree).
     # 4200 and 8705: 9 and 18 chunks of 512, i.e. merge nodes of 8 + 1 and 8 + 8 + 2 entries.
-    c = Case(8, 1, 128, 16, "bf16", [20000, 40000, 70000, 513, 4200, 8705], seed=35, amp_qk=0.3)
+    c = Case(8, 1, 128, 16, dtype, [20000, 40000, 70000, 513, 4200, 8705], seed=35, amp_qk=0.3)
     _, want = c.run_oracle()
     _, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
-    ok, err = within(got, want, "bf16")
+    ok, err = within(got, want, dtype)
     assert ok, err
-    assert err < 1e-4
+    assert err < (1e-4 if dtype == "bf16" else 1e-5)
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
@@ -407,18 +409,19 @@ def test_outputs_stored_straight_into_pinned_host_memory_have_the_staged_copys_b
         buf.free()
 
 
-def test_batch_invariance_when_ctas_stream_many_ragged_items(dev):
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_batch_invariance_when_ctas_stream_many_ragged_items(dev, dtype):
     # More (sequence, group) pairs than resident CTAs, lengths that are no multiple of anything:
     # every CTA streams several items, and most start at an arbitrary place of its tile stream.
     # A sequence's bits must still equal those it gets alone (one item, first in its CTA's stream).
     rng = np.random.default_rng(91)
     lengths = [int(x) for x in rng.integers(1, 900, size=360)]
-    full = Case(32, 4, 128, 16, "bf16", lengths, seed=92, amp_qk=0.3)
+    full = Case(32, 4, 128, 16, dtype, lengths, seed=92, amp_qk=0.3)
     _, out_full = full.run_device(dev, variant=qd.ATTN_SPLIT)
     assert np.all(np.isfinite(out_full))
     for t in (0, 7, 123, 359, int(np.argmax(full.lengths)), int(np.argmin(full.lengths))):
         n = int(full.lengths[t])
-        alone = Case(32, 4, 128, 16, "bf16", [n], seed=93, pool_blocks=full.pool_blocks)
+        alone = Case(32, 4, 128, 16, dtype, [n], seed=93, pool_blocks=full.pool_blocks)
         nb = (n + 15) // 16
         alone.blocks = full.blocks[full.table_at[t]:full.table_at[t] + nb].copy()
         alone.table_at[:] = 0
@@ -431,7 +434,7 @@ def test_batch_invariance_when_ctas_stream_many_ragged_items(dev):
 
 
 @pytest.mark.parametrize("dtype,heads,kvh,d,B", [("bf16", 32, 4, 128, 16), ("f16", 8, 2, 64, 32), ("bf16", 8, 1, 256, 16),
-                                                ("bf16", 24, 2, 128, 64)])
+                                                ("bf16", 24, 2, 128, 64), ("f32", 8, 2, 64, 16), ("f32", 16, 2, 128, 32)])
 def test_runs_of_chunks_do_not_change_a_single_bit(dev, dev_x, monkeypatch, dtype, heads, kvh, d, B):
     # Work items are runs of consecutive chunks of a sequence; how long the runs are is the
     # scheduler's choice per op.  Every chunk keeps its own state, so the outputs must not move.
