@@ -315,7 +315,7 @@ int32_t qvx_paged_attention_host(qvx_device *dev, qvx_buffer *pool, const qvx_ge
  * them pass through the library's pinned staging ring): give PINNED host memory
  * (cudaHostAlloc / cudaHostRegister) for the copies to be asynchronous; from pageable memory
  * the CUDA runtime stages each copy and the call blocks for as long, which serialises the ops.
- * A page-locked, 16-byte aligned out_host is not copied to at all: the attention kernel stores the
+ * An out_host page-locked under this device and 16-byte aligned is not copied to at all: the attention kernel stores the
  * outputs into it over the bus while it runs (both calls; the bytes are the same either way).
  * The host arrays must stay unchanged until the wait; out_host is written by then. */
 int32_t qvx_paged_attention_host_async(qvx_device *dev, qvx_buffer *pool, const qvx_geometry *geo,

@@ -956,14 +956,16 @@ static bool prelude_ok(const qvx_prelude* p) {
 // the new rows back into k_back / v_back.
 // The device's address for `bytes` of the caller's host array, or null when the device cannot reach it with plain
 // 16-byte stores: memory that is not page-locked, not mapped, or not 16-byte aligned.
-static float* mapped_host_pointer(const void* host, size_t bytes) {
+static float* mapped_host_pointer(const qvx_device* dev, const void* host, size_t bytes) {
     if (!host || ((uintptr_t)host & 15u)) return nullptr;
     cudaPointerAttributes at{}, end{};
     if (cudaPointerGetAttributes(&at, host) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     if (at.type != cudaMemoryTypeHost || !at.devicePointer) return nullptr;
+    // (memory page-locked under another device's context may not be mapped for this one: it takes the copy)
+    if (at.device != dev->ordinal) return nullptr;
     // (the whole range must be page-locked: look at its last byte as well)
     if (cudaPointerGetAttributes(&end, (const char*)host + bytes - 1) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    if (end.type != cudaMemoryTypeHost || !end.devicePointer) return nullptr;
+    if (end.type != cudaMemoryTypeHost || !end.devicePointer || end.device != dev->ordinal) return nullptr;
     if ((const char*)end.devicePointer - (const char*)at.devicePointer != (ptrdiff_t)(bytes - 1)) return nullptr;
     return (float*)at.devicePointer;
 }
@@ -1092,7 +1094,7 @@ static int32_t paged_attention_submit(qvx_device* dev, qvx_buffer* pool, const q
     // The outputs go straight into the caller's array when the device can address it (pinned memory, which
     // unified addressing maps into the device's address space): the kernel's stores cross the bus while it runs,
     // and the op needs no copy out.  Pageable (or misaligned) memory takes the staged copy.
-    float* d_out = s ? mapped_host_pointer(out, 4 * s * q_out) : nullptr;
+    float* d_out = s ? mapped_host_pointer(dev, out, 4 * s * q_out) : nullptr;
     const bool out_direct = d_out != nullptr;
     if (!out_direct) d_out = (float*)(ds + o_out);
     if (rc == QVX_OK && s)
