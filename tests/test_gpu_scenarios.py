@@ -385,6 +385,88 @@ def test_c4_churn_compaction_then_attention(dev):
     od.close()
 
 
+def test_c4_at_full_size_churn_and_compaction_keep_every_live_block(dev):
+    """The churn configuration at its own size: a pool of 65 536 blocks of 128 KiB (8 GiB) filled to 90 % by sequences
+    of U[256, 8192] positions, 5 % of the blocks retired and as many admitted per step, a compaction pass after each
+    step.  Size-independent properties instead of an oracle copy of 8 GiB: every live block's checksum follows it
+    to its new id (sequence by sequence, in table order), the live ids are exactly 0..L, nothing outside the moves'
+    destinations changes, and the counters add up."""
+    torch = pytest.importorskip("torch")
+    import ctypes as C
+    from qubivex_b200.device import ptr
+    from qubivex_b200.kvpool import KvPool
+    B, kvh, d, N = 32, 8, 128, 65536
+    geo = qd.geometry(B, kvh, d, qd.BF16)
+    bb = qd.block_bytes(geo)
+    assert bb == 128 * 1024
+    rng = np.random.default_rng(404)
+    kv = KvPool(geo, N)
+    kv.set_free_order(rng.permutation(N))
+    pool = torch.empty(N * bb, dtype=torch.uint8, device="cuda")
+    words = pool.view(torch.int64)
+    g = torch.Generator(device="cuda").manual_seed(405)
+    step_words = 1 << 27
+    for lo in range(0, words.numel(), step_words):
+        n = min(step_words, words.numel() - lo)
+        words[lo:lo + n] = torch.randint(-2**62, 2**62, (n,), dtype=torch.int64, device="cuda", generator=g)
+    checksums = lambda: words.view(N, -1).sum(dim=1).cpu().numpy()      # per block, wrapping
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def admit(blocks_wanted):
+        lens, have = [], 0
+        while have < blocks_wanted:
+            n = int(rng.integers(256, 8193))
+            lens.append(n)
+            have += (n + B - 1) // B
+        ms = [kv.mirror() for _ in lens]
+        plan = kv.attention_plan(ms, [n - 1 for n in lens], 0)
+        assert plan is not None
+        kv.commit(plan, ms, 0)
+        kv.free_plan(plan)
+        return ms
+
+    live = admit(int(0.9 * N))
+    used = lambda: int(kv.stats().blocks - kv.stats().free)
+    assert 0.9 * N <= used() <= 0.9 * N + 256
+    moved_total = 0
+    for _ in range(3):
+        # churn: retire sequences until 5 % of the pool's blocks are back, admit as many blocks again
+        target = used() - int(0.05 * N)
+        while used() > target:
+            live.pop(int(rng.integers(0, len(live)))).drop()
+        live += admit(int(0.9 * N) - used())
+        before = checksums()
+        tables = [m.blocks(0).copy() for m in live]
+        L = used()
+        src, dst = kv.compact()
+        assert len(src) > 0 and np.all(src >= L) and np.all(dst < L) and len(set(dst.tolist())) == len(dst)
+        d_src, d_dst = (torch.from_numpy(a.astype(np.int32)).cuda() for a in (src, dst))
+        dev.check(dev.lib.qvx_block_copy(dev.h, C.byref(geo), ptr(pool), N, ptr(d_src), ptr(d_dst), len(src), stream))
+        torch.cuda.synchronize()
+        dev.kernel_times()                                            # no late report
+        after = checksums()
+        seen = np.zeros(N, dtype=bool)
+        for m, old in zip(live, tables):
+            new = m.blocks(0)
+            assert len(new) == len(old) and np.all(new < L)
+            assert np.array_equal(after[new], before[old])           # the bytes went with the block, in table order
+            assert not seen[new].any()
+            seen[new] = True
+        assert seen[:L].all() and not seen[L:].any()                  # the live ids are exactly 0..L
+        untouched = np.ones(N, dtype=bool)
+        untouched[dst] = False
+        assert np.array_equal(after[untouched], before[untouched])    # (sources keep their bytes: they are free now)
+        assert used() == L
+        moved_total += len(src)
+    st = kv.stats()
+    assert st.compaction_moves == moved_total and st.bytes_moved == 2 * moved_total * bb   # a read and a write per move
+    assert moved_total > 0.05 * N     # (the first pass gathers a pool filled in random order: about a tenth of the live blocks)
+    for m in live:
+        m.drop()
+    assert kv.stats().free == N
+    kv.delete()
+
+
 # ---- the prelude inside the runtime's loop --------------------------------------------------------
 def test_decode_steps_from_raw_projections_keep_the_host_cache_in_step(dev):
     """Each pass hands the device the raw projections; clip, norms and RoPE run there and the new
