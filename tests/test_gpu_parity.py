@@ -667,6 +667,8 @@ def test_control_duplicate_sync_rows_written_in_the_other_order_are_noticed(dev)
 # ---- the benchmark configurations at their full sizes, sampled against the oracle ----------------------
 def _full_size_case(name):
     rng = np.random.default_rng(8)
+    if name == "c2":    # the configuration the metric is quoted on, one layer: batch 64, contexts U[1024, 4096], 32 q / 4 kv heads
+        return 32, 4, 128, 16, rng.integers(1024, 4097, size=64)
     if name == "c3":    # 16 x 32768 positions, 32 q / 4 kv heads of 128, block 16 (the prefix sharing is in test_gpu_scenarios)
         return 32, 4, 128, 16, np.full(16, 32768)
     if name == "c4":    # ~58 982 live blocks of 32 positions, 32 q / 8 kv heads: the work items are runs of four chunks
@@ -679,7 +681,7 @@ def _full_size_case(name):
     raise ValueError(name)
 
 
-@pytest.mark.parametrize("name", ["c3", "c4", "c5"])
+@pytest.mark.parametrize("name", ["c2", "c3", "c4", "c5"])
 def test_full_size_configurations_sampled_against_the_oracle(dev, name):
     """One attention step at the configuration's full size (up to 7.2 GiB of KV, hundreds of work items per CTA, runs of
     two to four chunks, merge trees of two levels), and the shortest, the median and the longest sequence checked against
