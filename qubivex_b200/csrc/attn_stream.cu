@@ -164,10 +164,11 @@ struct StreamSmem {
     // A multiple of CW: tile n goes to stage n % stages and to warp n % CW, so a stage is
     // always read by the same warp and a warp waits for its stages' phases strictly in order
     // (waiting two phases ahead on an mbarrier parity would return at once).
+    static constexpr uint32_t stages_most = (stages_fit > 4 * CW ? 4 * CW : stages_fit) / CW * CW;
 #ifdef QVX_MAX_STAGES  // experiments: a shallower ring
-    static constexpr uint32_t stages = QVX_MAX_STAGES;
+    static constexpr uint32_t stages = stages_most < QVX_MAX_STAGES ? stages_most : QVX_MAX_STAGES;
 #else
-    static constexpr uint32_t stages = (stages_fit > 4 * CW ? 4 * CW : stages_fit) / CW * CW;
+    static constexpr uint32_t stages = stages_most;
 #endif
     static constexpr uint32_t ring_off = 0;
     static constexpr uint32_t res_off = stages * stage_bytes;
@@ -1184,7 +1185,9 @@ template <int DT, int D, int VAR>
 static int32_t launch_stream(qvx_device* dev, const StreamArgs& a, cudaStream_t s) {
     using SM = StreamSmem<D, (DT == QVX_F32 ? 4 : 2)>;
     // (the cross-chunk merge stages a node's entries in the ring, sized by the 16-bit layout's)
+#ifndef QVX_MAX_STAGES
     static_assert(SM::stages * SM::stage_bytes >= MERGE_FAN * (8 * D + 16) * 4 || D > 128, "the ring holds a merge node's entries");
+#endif
     auto kernel = attn_stream_kernel<DT, D, VAR>;
     static int per_device[64] = {};  // set up once per device (the attribute belongs to the device's context)
     int& ctas_per_sm = per_device[dev->ordinal & 63];
