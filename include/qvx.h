@@ -211,7 +211,8 @@ int32_t qvx_kv_append_attn_decode(qvx_device *dev, qvx_tables *tables, void *poo
  * the scratch is a fixed array inside the library: 16 MiB of partial results + 16384
  * arrival counters, held on every GPU that loads the library until the process exits.
  * An op that needs more ((sequences x head groups) > 16384, or
- * sequences x head groups x ceil((max_pos + 1) / 512) x (8 * head_dim + 16) x 4 bytes > 16 MiB)
+ * sequences x head groups x ceil((max_pos + 1) / chunk) x (8 * head_dim + 16) x 4 bytes > 16 MiB, chunk = 576
+ * positions rounded down to whole blocks, as in qvx_attn_decode)
  * returns QVX_ERR_UNSUPPORTED with the sizes in qvx_last_error.  bf16 or f16 pools in the native
  * layout, head_dim 64 or 128.  The first call on a device looks the array's address up: make
  * that call outside any stream capture.  All calls share the array: calls that overlap on

@@ -17,13 +17,13 @@
 //
 // Same arithmetic as the main 16-bit kernel: S^T = K Q^T and O^T = V^T P^T on the tensor cores,
 // queries and probabilities as value + remainder for bf16, online softmax in base 2, the context
-// split into chunks of 512 positions, the chunks of a sequence merged in chunk order by the CTA
+// split into the main kernel's chunks (576 positions in whole blocks; no doubling for long sequences), the chunks of a
+// sequence merged in chunk order by the CTA
 // that delivers the last one.  There is no counterpart in the reference.
 #include "attn_ptx.cuh"
 
 namespace qvx {
 
-constexpr uint32_t STATIC_CHUNK_TOKENS = 512;
 constexpr uint32_t STATIC_MAX_COUNTERS = 16384;                       // (sequence, group) pairs per call
 constexpr size_t STATIC_PARTIAL_BYTES = 16u << 20;                    // partial results per call
 constexpr size_t STATIC_SCRATCH_BYTES = STATIC_PARTIAL_BYTES + STATIC_MAX_COUNTERS * 4;
@@ -45,7 +45,7 @@ struct StaticArgs {
     const uint32_t* table_at;
     int* status;
     uint64_t block_bytes;
-    uint32_t page_bytes, tiles_per_block, heads, group, groups_per_kv, ngroups, max_chunks, chunk_blocks;
+    uint32_t page_bytes, tiles_per_block, heads, group, groups_per_kv, ngroups, max_chunks, chunk_blocks, chunk_tokens;
     float scale_log2;
 };
 
@@ -70,13 +70,13 @@ __global__ void __launch_bounds__(STHREADS, 3) attn_static_kernel(StaticArgs a) 
     const uint32_t g = lane >> 2, t = lane & 3;
     const uint32_t chunk = blockIdx.x, grp = blockIdx.y, seq = blockIdx.z;
     const uint32_t len = a.pos[seq] + 1u;
-    const uint32_t nch = (len + STATIC_CHUNK_TOKENS - 1) / STATIC_CHUNK_TOKENS;
+    const uint32_t nch = (len + a.chunk_tokens - 1) / a.chunk_tokens;
     if (chunk >= nch) return;
     if (nch > a.max_chunks) {  // the caller's bound on the positions was too small: refuse, write nothing
         if (threadIdx.x == 0) atomicExch(a.status, STATUS_POSITION_BOUND);
         return;
     }
-    const uint32_t tokens = min(STATIC_CHUNK_TOKENS, len - chunk * STATIC_CHUNK_TOKENS);
+    const uint32_t tokens = min(a.chunk_tokens, len - chunk * a.chunk_tokens);
     const uint32_t kv_head = grp / a.groups_per_kv, sub = grp % a.groups_per_kv;
     const uint32_t head0 = kv_head * a.group + sub * 8, nheads = min(8u, a.group - sub * 8);
     const uint32_t first = a.table_at[seq] + chunk * a.chunk_blocks;
@@ -231,17 +231,16 @@ extern "C" int32_t qvx_attn_decode_static(qvx_device* dev, const qvx_geometry* g
     if (!geometry_ok(geo)) return fail(dev, QVX_ERR_UNSUPPORTED, "cuda backend has no KV pool of this geometry");
     std::lock_guard<std::mutex> lk(dev->mu);
     const Layout L = make_layout(geo);
-    if (L.layout != QVX_LAYOUT_NATIVE || L.dtype == QVX_F32 || (L.d != 64 && L.d != 128) || L.B % TILE != 0 ||
-        STATIC_CHUNK_TOKENS % L.B != 0)
+    if (L.layout != QVX_LAYOUT_NATIVE || L.dtype == QVX_F32 || (L.d != 64 && L.d != 128) || L.B % TILE != 0 || L.B > 512)
         return fail(dev, QVX_ERR_UNSUPPORTED,
-                    "qvx_attn_decode_static: native layout, bf16 or f16, head_dim 64 or 128, block_tokens a multiple of 16 dividing %u",
-                    STATIC_CHUNK_TOKENS);
+                    "qvx_attn_decode_static: native layout, bf16 or f16, head_dim 64 or 128, block_tokens a multiple of 16 up to 512");
+    const uint32_t chunk_tokens = base_chunk_tokens(CHUNK_BASE_TOKENS, L.B);
     if (heads == 0 || heads % L.kvh != 0)
         return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: %zu tokens, %zu heads, %u KV heads of %u", s,
                     heads, L.kvh, L.d);
     if (s == 0) return QVX_OK;
     const uint32_t group = (uint32_t)(heads / L.kvh), gpk = (group + 7) / 8, ngroups = L.kvh * gpk;
-    const uint64_t max_chunks = ((uint64_t)max_pos + STATIC_CHUNK_TOKENS) / STATIC_CHUNK_TOKENS;
+    const uint64_t max_chunks = ((uint64_t)max_pos + chunk_tokens) / chunk_tokens;
     const uint64_t pairs = (uint64_t)s * ngroups;
     const uint64_t need = pairs * max_chunks * (8ull * L.d + 16) * 4;
     if (s > 65535 || ngroups > 65535 || max_chunks > 1000 || pairs > STATIC_MAX_COUNTERS || need > STATIC_PARTIAL_BYTES)
@@ -281,7 +280,7 @@ extern "C" int32_t qvx_attn_decode_static(qvx_device* dev, const qvx_geometry* g
     a.pos = pos; a.blocks = blocks; a.table_at = table_at; a.status = device_status_word(dev);
     a.block_bytes = L.block_bytes; a.page_bytes = L.page_bytes; a.tiles_per_block = L.B / TILE;
     a.heads = (uint32_t)heads; a.group = group; a.groups_per_kv = gpk; a.ngroups = ngroups;
-    a.max_chunks = (uint32_t)max_chunks; a.chunk_blocks = STATIC_CHUNK_TOKENS / L.B;
+    a.max_chunks = (uint32_t)max_chunks; a.chunk_blocks = chunk_tokens / L.B; a.chunk_tokens = chunk_tokens;
     a.scale_log2 = (1.0f / sqrtf((float)L.d)) * 1.4426950408889634f;
     dim3 grid((unsigned)max_chunks, ngroups, (unsigned)s);
     e = cudaErrorInvalidValue;

@@ -202,6 +202,12 @@ int32_t launch_kv_rows(qvx_device* dev, const Layout& L, void* pool, const float
                        size_t pool_blocks, int kind, cudaStream_t s);
 int32_t launch_attn_prelude(qvx_device* dev, const Layout& L, size_t heads, size_t s, float* q, float* k_new, float* v_new,
                             const qvx_prelude* p, cudaStream_t stream);
+// The positions of one chunk -- the unit of the online softmax -- before long sequences double it: 576 rounded down to
+// whole blocks (at least one block).  One rule for the streaming kernel and the fixed-scratch one: same chunks, same bits
+// per chunk.
+constexpr uint32_t CHUNK_BASE_TOKENS = 576;
+inline uint32_t base_chunk_tokens(uint32_t base, uint32_t B) { return (base > B ? base : B) / B * B; }
+
 int32_t launch_block_copy(qvx_device* dev, const Layout& L, void* pool, const uint32_t* src,
                           const uint32_t* dst, size_t n, size_t pool_blocks, cudaStream_t s);
 

@@ -113,7 +113,7 @@ def test_nan_and_inf_keys_follow_the_reference(dev):
     ("bf16", 8, 1, 256, 16), ("f16", 32, 4, 128, 16), ("f16", 4, 2, 64, 64), ("bf16", 64, 8, 128, 256),
 ])
 def test_split_attention_is_within_tolerance(dev, dtype, heads, kvh, d, B):
-    lengths = [1, 2, 15, 16, 17, 255, 256, 257, 511, 700, 1023, 1500]
+    lengths = [1, 2, 15, 16, 17, 255, 256, 257, 511, 575, 576, 577, 700, 1023, 1152, 1153, 1500]
     c = Case(heads, kvh, d, B, dtype, lengths, seed=31, fill=0xFF)  # 0xFF bytes are NaNs: tails must be masked
     want_pool, want = c.run_oracle()
     got_pool, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
@@ -125,10 +125,10 @@ def test_split_attention_is_within_tolerance(dev, dtype, heads, kvh, d, B):
 
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_long_contexts_take_larger_chunks_and_a_merge_tree(dev, dtype):
-    # 20000 positions: 1024-position chunks; 40000 and 70000: 2048-position chunks, the last
-    # with more than 32 of them (two levels of the fan-in-8 merge tree).
-    # 4200 and 8705: 9 and 18 chunks of 512, i.e. merge nodes of 8 + 1 and 8 + 8 + 2 entries.
-    c = Case(8, 1, 128, 16, dtype, [20000, 40000, 70000, 513, 4200, 8705], seed=35, amp_qk=0.3)
+    # 20000, 40000 and 70000 positions: 1152-position chunks, 18, 35 and 61 of them (two levels of the fan-in-8
+    # merge tree, the last with a second-level node of 8 entries).  577: two chunks.
+    # 4700 and 9800: 9 and 18 chunks of 576, i.e. merge nodes of 8 + 1 and 8 + 8 + 2 entries.
+    c = Case(8, 1, 128, 16, dtype, [20000, 40000, 70000, 577, 4700, 9800], seed=35, amp_qk=0.3)
     _, want = c.run_oracle()
     _, got = c.run_device(dev, variant=qd.ATTN_SPLIT)
     ok, err = within(got, want, dtype)
@@ -438,7 +438,7 @@ def test_batch_invariance_when_ctas_stream_many_ragged_items(dev, dtype):
 def test_runs_of_chunks_do_not_change_a_single_bit(dev, dev_x, monkeypatch, dtype, heads, kvh, d, B):
     # Work items are runs of consecutive chunks of a sequence; how long the runs are is the
     # scheduler's choice per op.  Every chunk keeps its own state, so the outputs must not move.
-    lengths = [3000, 513, 2048, 1, 1537, 4096, 700, 2049] * 3
+    lengths = [3000, 577, 2304, 1, 1729, 4096, 700, 2305] * 3
     c = Case(heads, kvh, d, B, dtype, lengths, seed=95, amp_qk=0.4)
     outs = {}
     for run in ("1", "2", "3", "4"):
@@ -458,7 +458,7 @@ def test_a_step_appended_inside_a_run_lands_in_the_pool(dev_x, monkeypatch):
     # item holds several chunks.  Pool bytes and outputs against the oracle, runs of 1 and of 4.
     import ctypes as C
     import torch
-    lengths = [2500, 1025, 4096, 512, 513]
+    lengths = [2500, 1153, 4096, 576, 577]
     c = Case(32, 4, 128, 16, "bf16", lengths, seed=97, amp_qk=0.4)
     want_pool, want = c.run_oracle()
     for run in ("1", "4"):

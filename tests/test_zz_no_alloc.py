@@ -89,7 +89,7 @@ def test_two_calls_in_a_row_match_the_ordinary_entry_point():
     dev = qd.CudaDevice(0)
     try:
         # first call: sequences of one chunk and of several, a ragged tail, a single position
-        _close(_case(dev, torch, 1, [1, 17, 511, 512, 513, 1300, 4096], first_launch=True))
+        _close(_case(dev, torch, 1, [1, 17, 511, 512, 513, 575, 576, 577, 1300, 4096], first_launch=True))
         # second call at once, other shapes: it finds the array as the first call left it
         _close(_case(dev, torch, 2, [2048, 700, 33, 3000], heads=16, kvh=4, d=64, B=32, dtype=qd.F16, first_launch=True))
         _close(_case(dev, torch, 3, [900, 1025], heads=8, kvh=2))                 # groups of 4 query heads
