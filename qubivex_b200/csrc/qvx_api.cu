@@ -338,9 +338,10 @@ static int32_t validate_tables(qvx_device* dev, const Layout& L, size_t pool_blo
                     s, heads, L.kvh, L.d);
     if (s > 65535) return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: %zu tokens in one op (at most 65535)", s);
     if (n_blocks > 0x7fffffffu) return fail(dev, QVX_ERR_CORE, "block tables of %zu entries", n_blocks);
-    for (size_t i = 0; i < n_blocks; i++)
-        if (blocks[i] >= pool_blocks)
-            return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: a block past the pool's %zu", pool_blocks);
+    uint32_t top = 0;  // (a running maximum, no branch per id: this loop is on every op's way to its first copy)
+    for (size_t i = 0; i < n_blocks; i++) top = blocks[i] > top ? blocks[i] : top;
+    if (n_blocks && top >= pool_blocks)
+        return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: a block past the pool's %zu", pool_blocks);
     for (size_t t = 0; t < s; t++)
         if ((size_t)table_at[t] + pos[t] / L.B >= n_blocks)
             return fail(dev, QVX_ERR_SHAPE, "shape mismatch in routed moe attention: token %zu has no block for position %u",
