@@ -83,12 +83,37 @@ def bind_near_gpu(local_rank: int) -> str:
         words = pynvml.nvmlDeviceGetCpuAffinity(h, (max(allowed) + 64) // 64)
         near = {64 * w + b for w, bits in enumerate(words) for b in range(64) if (int(bits) >> b) & 1}
         mine = near & allowed
+        memory = prefer_memory_near_gpu(pynvml, h)
         if not mine or mine == allowed:
-            return f"unchanged ({len(allowed)} cores allowed, {len(near)} next to the GPU)"
+            return f"cores unchanged ({len(allowed)} allowed, {len(mine)} of them next to the GPU); {memory}"
         os.sched_setaffinity(0, mine)
-        return f"{len(mine)} of {len(allowed)} allowed cores: those next to the GPU"
+        return f"{len(mine)} of {len(allowed)} allowed cores: those next to the GPU; {memory}"
     except Exception as e:  # no NVML, an old torch, a restricted container: the run goes on unbound
         return f"unchanged ({type(e).__name__})"
+
+
+def prefer_memory_near_gpu(pynvml, handle) -> str:
+    """The process's memory policy: prefer the NUMA node the GPU hangs off (what `numactl --preferred` does), so that
+    the page-locked buffers allocated from here on are on that node even when the cores the container allows are on
+    the other socket -- a rank whose copies cross the sockets' link shares it with every other such rank."""
+    import ctypes
+    try:
+        words = pynvml.nvmlDeviceGetMemoryAffinity(handle, 1, pynvml.NVML_AFFINITY_SCOPE_NODE)
+        mask = int(words[0])
+        if not mask:
+            return "memory policy unchanged (no node reported)"
+        node = (mask & -mask).bit_length() - 1
+        libc = ctypes.CDLL(None, use_errno=True)
+        nodemask = ctypes.c_ulong(1 << node)
+        SYS_set_mempolicy, MPOL_PREFERRED = 238, 1       # x86-64
+        if os.uname().machine != "x86_64":
+            return "memory policy unchanged (not x86-64)"
+        rc = libc.syscall(SYS_set_mempolicy, MPOL_PREFERRED, ctypes.byref(nodemask), 65)
+        if rc != 0:
+            return f"memory policy unchanged (set_mempolicy: errno {ctypes.get_errno()})"
+        return f"memory preferred on node {node}"
+    except Exception as e:
+        return f"memory policy unchanged ({type(e).__name__})"
 
 
 def config_of(shape: "wl.Shape", layers: int) -> dict:
@@ -447,6 +472,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     e2e_value, each_ms = time_host(W + K, False)
     x1 = dev.transfers()
     ops = max(1, x1.submissions - x0.submissions)
+    if dist is not None:   # every rank's answer, in rank order
+        every = [None] * world
+        dist.all_gather_object(every, host_cores)
+        host_cores = every
     host_us = {"submit_us_per_op": (x1.submit_ns - x0.submit_ns) / ops / 1e3, "wait_us_per_op": (x1.wait_ns - x0.wait_ns) / ops / 1e3,
                "what": "host time inside qvx_paged_attention_host per layer: queueing the copies and kernels, then waiting for the stream",
                "cores": host_cores}
